@@ -1,0 +1,90 @@
+// Shared device helpers and the error channel of the kernel library.
+//
+// Every launcher is `extern "C"`, takes raw device pointers and a stream, allocates
+// nothing unless it says so, and returns 0 on success or a negative code after storing a
+// message that `b200_last_error()` returns.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#define B200_API extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with the Python side.
+enum : int { DTYPE_F32 = 0, DTYPE_BF16 = 1 };
+
+// Bits a kernel may set in the device-side error word it is handed.
+enum : int {
+  ERRBIT_BAD_PAGE = 1,      // a block-table entry was negative or past the arena
+  ERRBIT_BAD_TOKEN = 2,     // a token id was outside the embedding table
+  ERRBIT_BAD_POSITION = 4,  // a position did not fit the block table
+};
+
+int b200_fail(const char* fmt, ...);
+int b200_check_launch(const char* what);
+
+#define B200_REQUIRE(cond, ...)                 \
+  do {                                          \
+    if (!(cond)) return b200_fail(__VA_ARGS__); \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats. Every thread gets the
+// result, and the order of additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = (lane < warps) ? scratch[lane] : 0.f;
+  total = warp_sum(total);
+  return total;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = (lane < warps) ? scratch[lane] : -INFINITY;
+  total = warp_max(total);
+  return total;
+}
+
+// Offset (in elements) of row `row` of kv head `head` in page `page` of one layer's K or V
+// arena laid out [pages][kv_heads][page_size][head_dim].
+__device__ __forceinline__ int64_t kv_row_offset(int page, int head, int row, int kv_heads,
+                                                 int page_size, int head_dim) {
+  return ((static_cast<int64_t>(page) * kv_heads + head) * page_size + row) * head_dim;
+}

@@ -1,0 +1,125 @@
+// Embedding gather, RMSNorm (with the residual add fused in) and SwiGLU's gate.
+//
+// The residual stream is kept in 32-bit in both precisions; norms, the residual sum and
+// the activation are computed in 32-bit and rounded once on the way out.
+#include "common.cuh"
+
+// out[t, :] = table[ids[t], :]  (reference: cuda/kernels.cu:59-68, one row per block here)
+template <typename T>
+__global__ void embedding_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                        float* __restrict__ out, int hidden, int vocab,
+                                        int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + static_cast<int64_t>(t) * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_TOKEN);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + static_cast<int64_t>(id) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+B200_API int b200_embedding_gather(const void* table, int table_dtype, const int* ids, float* out,
+                                   int tokens, int hidden, int vocab, int* err,
+                                   cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  B200_REQUIRE(tokens > 0 && hidden > 0 && vocab > 0, "embedding_gather: bad sizes");
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == DTYPE_F32) {
+    embedding_gather_kernel<float><<<tokens, threads, 0, stream>>>(
+        static_cast<const float*>(table), ids, out, hidden, vocab, err);
+  } else if (table_dtype == DTYPE_BF16) {
+    embedding_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, err);
+  } else {
+    return b200_fail("embedding_gather: unknown dtype %d", table_dtype);
+  }
+  return b200_check_launch("embedding_gather");
+}
+
+// RMSNorm of row r of the residual stream x (32-bit), optionally after adding the pending
+// branch output `delta` to it:  v = x[r] + delta[r];  y = v * rsqrt(mean(v^2) + eps) * w.
+// With `rows` == nullptr every row is normed and v is written back to x; with `rows` the
+// kernel norms only x[rows[i]] into out[i] and leaves x alone (the model's last norm, which
+// only the wanted positions need). Formula: python/instinct/backends/portable.py:144-149;
+// the fused add follows cuda/kernels.cu:85-98 but keeps the sum in 32-bit.
+template <typename T>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                               const float* __restrict__ weight, T* __restrict__ out,
+                               const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+  float* xr = x + static_cast<int64_t>(r) * hidden;
+  const T* dr = delta ? delta + static_cast<int64_t>(r) * hidden : nullptr;
+  T* outr = out + static_cast<int64_t>(blockIdx.x) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) {
+      v += to_f32<T>(dr[i]);
+      if (!rows) xr[i] = v;
+    }
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    if (dr && rows) v += to_f32<T>(dr[i]);
+    outr[i] = from_f32<T>(v * inv * weight[i]);
+  }
+}
+
+B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void* out,
+                          const int* rows, int num_rows, int hidden, float eps, int dtype,
+                          cudaStream_t stream) {
+  if (num_rows == 0) return 0;
+  B200_REQUIRE(num_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (dtype == DTYPE_F32) {
+    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
+        x, static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
+  } else if (dtype == DTYPE_BF16) {
+    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
+        x, static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out),
+        rows, hidden, eps);
+  } else {
+    return b200_fail("rmsnorm: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("rmsnorm");
+}
+
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i],  silu(g) = g / (1 + exp(-g))
+// (python/instinct/backends/dense.py:124-128; cuda/kernels.cu:100-106).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                                int64_t total) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t t = idx / inter;
+  const int i = static_cast<int>(idx - t * inter);
+  const float g = to_f32<T>(gu[t * 2 * inter + i]);
+  const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+  out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+B200_API int b200_silu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype,
+                           cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  B200_REQUIRE(tokens > 0 && inter > 0, "silu_mul: bad sizes");
+  const int64_t total = static_cast<int64_t>(tokens) * inter;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  if (dtype == DTYPE_F32) {
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up),
+                                                          static_cast<float*>(out), inter, total);
+  } else if (dtype == DTYPE_BF16) {
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
+  } else {
+    return b200_fail("silu_mul: unknown dtype %d", dtype);
+  }
+  return b200_check_launch("silu_mul");
+}

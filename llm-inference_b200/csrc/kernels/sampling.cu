@@ -1,0 +1,268 @@
+// Choosing the next token from 32-bit logits, one block per row.
+//
+// Greedy rows take the arg-max, lowest index on ties (cuda/kernels.cu:327-348). Sampled rows
+// follow python/instinct/sampling.py:47-101: candidates are the `kCandidates` largest logits;
+// probabilities are softmax(logit / temperature) over the candidates; a candidate survives
+// when its rank is below top_k, its probability is at least min_p times the largest, and
+// the probability mass of strictly larger logits is below top_p; one survivor is drawn in
+// proportion to its probability. Instead of sorting, thresholds are found by a radix search
+// over the logits' bit patterns (counts for ranks, fixed-point mass for top_p), so equal
+// logits are kept or dropped together. The draw uses a counter-based generator keyed per
+// row, so a seeded request gets the same tokens whatever else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kSampleThreads = 1024;
+constexpr int kCandidates = 1024;
+
+// Monotone map from float to unsigned: larger float <=> larger key.
+__device__ __forceinline__ uint32_t float_key(float v) {
+  const uint32_t bits = __float_as_uint(v);
+  return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+argmax_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
+                   const int* __restrict__ row_index, int* __restrict__ out) {
+  __shared__ float best_v[32];
+  __shared__ int best_i[32];
+  const int src_row = row_index ? row_index[blockIdx.x] : blockIdx.x;
+  const float* row = logits + src_row * row_stride;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  if (bi == 0x7fffffff) { bi = threadIdx.x < vocab ? threadIdx.x : 0; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int warps = blockDim.x >> 5;
+    bv = lane < warps ? best_v[lane] : -INFINITY;
+    bi = lane < warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[src_row] = bi;
+  }
+}
+
+// The key of the k-th largest element (1-based), found byte by byte from the top.
+__device__ uint32_t kth_largest_key(const float* __restrict__ row, int vocab, int k,
+                                    unsigned int* hist /* [256] shared */) {
+  uint32_t prefix = 0, mask = 0;
+  int remaining = k;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const uint32_t key = float_key(row[i]);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+    }
+    __syncthreads();
+    // Every thread walks the 256 bins the same way; cheap next to the scan above.
+    int bin = 255;
+    int above = 0;
+    for (; bin > 0; --bin) {
+      const int c = static_cast<int>(hist[bin]);
+      if (above + c >= remaining) break;
+      above += c;
+    }
+    remaining -= above;
+    prefix |= static_cast<uint32_t>(bin) << shift;
+    mask |= 0xffu << shift;
+    __syncthreads();
+  }
+  return prefix;
+}
+
+// Key K such that keeping keys >= K keeps exactly the candidates whose strictly-larger mass
+// is below `limit` (fixed-point). Only keys >= `floor_key` are candidates.
+__device__ uint32_t top_p_key(const float* __restrict__ row, int vocab, float inv_temp,
+                              float scaled_max, uint32_t floor_key, unsigned long long limit,
+                              unsigned long long* mass /* [256] shared */) {
+  uint32_t prefix = 0, mask = 0;
+  unsigned long long above_total = 0;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) mass[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = row[i];
+      const uint32_t key = float_key(v);
+      if (key >= floor_key && (key & mask) == prefix) {
+        const float p = expf(v * inv_temp - scaled_max);
+        atomicAdd(&mass[(key >> shift) & 0xffu],
+                  static_cast<unsigned long long>(p * 1099511627776.0f /* 2^40 */));
+      }
+    }
+    __syncthreads();
+    int bin = 255;
+    unsigned long long above = above_total;
+    for (; bin > 0; --bin) {
+      const unsigned long long c = mass[bin];
+      if (above + c >= limit) break;
+      above += c;
+    }
+    above_total = above;
+    prefix |= static_cast<uint32_t>(bin) << shift;
+    mask |= 0xffu << shift;
+    __syncthreads();
+  }
+  return prefix;
+}
+
+__global__ void __launch_bounds__(kSampleThreads)
+sample_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
+                   const float* __restrict__ temperature, const float* __restrict__ top_p,
+                   const float* __restrict__ min_p, const int* __restrict__ top_k,
+                   const unsigned long long* __restrict__ keys, const int* __restrict__ row_index,
+                   int* __restrict__ out) {
+  __shared__ float scratch[32];
+  __shared__ unsigned int hist[256];
+  __shared__ unsigned long long mass[256];
+  __shared__ float partial[kSampleThreads];
+  __shared__ int chosen;
+
+  const int r = blockIdx.x;
+  const int src_row = row_index ? row_index[r] : r;
+  const float* row = logits + src_row * row_stride;
+  const float temp = temperature[r];
+  const float inv_temp = 1.f / temp;
+  const int tid = threadIdx.x;
+
+  float local_max = -INFINITY;
+  for (int i = tid; i < vocab; i += blockDim.x) local_max = fmaxf(local_max, row[i]);
+  const float max_logit = block_max(local_max, scratch);
+  const float scaled_max = max_logit * inv_temp;
+
+  // Candidates: the kCandidates largest logits.
+  uint32_t keep_key = 0;
+  if (vocab > kCandidates) keep_key = kth_largest_key(row, vocab, kCandidates, hist);
+  const uint32_t candidate_key = keep_key;
+  const int k = top_k[r];
+  if (k > 0 && k < min(vocab, kCandidates)) {
+    keep_key = max(keep_key, kth_largest_key(row, vocab, k, hist));
+  }
+
+  // Softmax denominator over the candidates.
+  float local_sum = 0.f;
+  for (int i = tid; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (float_key(v) >= candidate_key) local_sum += expf(v * inv_temp - scaled_max);
+  }
+  const float denom = block_sum(local_sum, scratch);
+
+  const float mp = min_p[r];
+  if (mp > 0.f) {
+    // p >= min_p * p_max  <=>  exp(logit / T - max / T) >= min_p; the survivors are the keys
+    // at or above the smallest surviving logit's key.
+    uint32_t local_key = 0xffffffffu;
+    for (int i = tid; i < vocab; i += blockDim.x) {
+      const float v = row[i];
+      if (expf(v * inv_temp - scaled_max) >= mp) local_key = min(local_key, float_key(v));
+    }
+    if (tid == 0) hist[0] = 0xffffffffu;
+    __syncthreads();
+    atomicMin(&hist[0], local_key);
+    __syncthreads();
+    keep_key = max(keep_key, hist[0]);
+    __syncthreads();
+  }
+  const float tp = top_p[r];
+  if (tp < 1.f) {
+    const unsigned long long limit =
+        static_cast<unsigned long long>(static_cast<double>(tp) * static_cast<double>(denom) *
+                                        1099511627776.0);
+    keep_key = max(keep_key, top_p_key(row, vocab, inv_temp, scaled_max, candidate_key, limit, mass));
+  }
+
+  // Draw among the survivors in index order: thread `tid` owns a contiguous slice.
+  const int per = (vocab + blockDim.x - 1) / blockDim.x;
+  const int begin = min(vocab, tid * per), end = min(vocab, begin + per);
+  float mine = 0.f;
+  for (int i = begin; i < end; ++i) {
+    const float v = row[i];
+    if (float_key(v) >= keep_key) mine += expf(v * inv_temp - scaled_max);
+  }
+  partial[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.f;
+    for (int i = 0; i < blockDim.x; ++i) total += partial[i];
+    const uint64_t bits = splitmix64(keys[r]);
+    const float u = static_cast<float>(bits >> 40) * (1.0f / 16777216.0f);
+    const float target = u * total;
+    // The owner is the first slice whose cumulative mass passes the target; rounding can
+    // leave the target at the very top, in which case the last slice with survivors owns it.
+    float running = 0.f, base = 0.f;
+    int owner = -1;
+    for (int i = 0; i < blockDim.x; ++i) {
+      if (partial[i] > 0.f) {
+        owner = i;
+        base = running;
+        if (running + partial[i] > target) break;
+        running += partial[i];
+      }
+    }
+    int pick = -1;
+    if (owner >= 0) {
+      const int b = min(vocab, owner * per), e = min(vocab, b + per);
+      float acc = base;
+      for (int i = b; i < e; ++i) {
+        const float v = row[i];
+        if (float_key(v) >= keep_key) {
+          pick = i;
+          acc += expf(v * inv_temp - scaled_max);
+          if (acc > target) break;
+        }
+      }
+    }
+    chosen = pick;
+  }
+  __syncthreads();
+  if (tid == 0) out[src_row] = chosen >= 0 ? chosen : 0;
+}
+
+}  // namespace
+
+B200_API int b200_argmax_rows(const float* logits, int rows, int vocab, int64_t row_stride,
+                              const int* row_index, int* out, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "argmax_rows: bad sizes");
+  argmax_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, row_stride, row_index,
+                                                          out);
+  return b200_check_launch("argmax_rows");
+}
+
+// Row r of the call reads logits row `row_index[r]` (or r when row_index is null) and writes
+// the token to out[that row], so greedy and sampled rows of one batch can share `out`.
+// `keys[r]` seeds the row's single uniform draw.
+B200_API int b200_sample_rows(const float* logits, int rows, int vocab, int64_t row_stride,
+                              const float* temperature, const float* top_p, const float* min_p,
+                              const int* top_k, const unsigned long long* keys,
+                              const int* row_index, int* out, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  B200_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "sample_rows: bad sizes");
+  sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, row_stride, temperature,
+                                                          top_p, min_p, top_k, keys, row_index, out);
+  return b200_check_launch("sample_rows");
+}

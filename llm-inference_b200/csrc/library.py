@@ -1,0 +1,108 @@
+"""ctypes bindings of the CUDA kernel library.
+
+The library is hand-written CUDA for sm_100a with a C interface; it is compiled on first use
+and loaded from the source tree. There is no fallback: if it cannot be built or loaded,
+:func:`kernels` raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+from functools import lru_cache
+
+import torch
+
+from . import build
+
+DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1}
+
+ERROR_BITS = {
+    1: "a block-table entry was negative or past the cache arena",
+    2: "a token id was outside the embedding table",
+    4: "a position did not fit the block table",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODES[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def ptr(tensor: torch.Tensor | None) -> c_void_p:
+    if tensor is None:
+        return c_void_p(0)
+    return c_void_p(tensor.data_ptr())
+
+
+def stream_handle() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_SIGNATURES: dict[str, list] = {
+    "b200_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "b200_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "b200_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "b200_rope_kv_write": [c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 8 + [c_void_p, c_void_p],
+    "b200_paged_attention_plain": [c_void_p] * 6
+    + [c_int, c_int, c_void_p]
+    + [c_int] * 6
+    + [c_float, c_int, c_void_p, c_void_p],
+    "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
+    "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p],
+    "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p],
+}
+
+
+class KernelLibrary:
+    def __init__(self, path: str) -> None:
+        self.path = path
+        self.lib = ctypes.CDLL(path)
+        self.lib.b200_last_error.restype = ctypes.c_char_p
+        self.lib.b200_abi_version.restype = c_int
+        self._functions = {}
+        for name, argtypes in _SIGNATURES.items():
+            self.bind(name, argtypes)
+
+    def bind(self, name: str, argtypes: list) -> None:
+        try:
+            fn = getattr(self.lib, name)
+        except AttributeError:
+            raise KernelError(f"{self.path} does not export {name}") from None
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        self._functions[name] = fn
+
+    def has(self, name: str) -> bool:
+        return hasattr(self.lib, name)
+
+    def call(self, name: str, *args) -> None:
+        status = self._functions[name](*args)
+        if status != 0:
+            raise KernelError(self.lib.b200_last_error().decode(errors="replace"))
+
+
+@lru_cache(maxsize=1)
+def kernels() -> KernelLibrary:
+    """The loaded kernel library; builds it first if the sources changed."""
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "the engine's kernels are CUDA code for sm_100a and no CUDA device is visible; "
+            "there is no CPU path"
+        )
+    return KernelLibrary(str(build.build_kernels()))
+
+
+def check_error_word(word: torch.Tensor, where: str) -> None:
+    """Raise if a kernel set a bit in the device error word (this synchronises)."""
+    value = int(word.item())
+    if value:
+        reasons = [text for bit, text in ERROR_BITS.items() if value & bit]
+        word.zero_()
+        raise KernelError(f"{where}: " + "; ".join(reasons or [f"error bits {value}"]))

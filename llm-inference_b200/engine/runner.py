@@ -1,0 +1,245 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+:class:`ModelRunner.step` is the only way tokens reach the model. Generation, the replay
+tool and the benchmark all call it. A step takes any mix of prompt portions and single
+decoded tokens, cut anywhere; it runs exactly the tokens it is given against the cache
+that earlier steps left, writes their keys and values, and returns 32-bit logits at the
+wanted places. The reference runs decode and prefill as separate passes per step
+(python/instinct/mlx_engine.py:404-425) over ``DecodeBatch`` / ``PrefillBatch``
+(python/instinct/batches.py:27-253); here both are rows of one flattened batch.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.paged_cache import PagedCache
+from ..csrc.library import check_error_word, kernels
+from ..parts.context import HostBatch, StepContext, Workspace
+from ..parts.model import LayerCall, Model
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens and the places among them whose logits are wanted."""
+
+    request_id: int
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class _Staging:
+    """Host (pinned) and device int32 buffers the step's metadata travels in, as one copy."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.capacity = 0
+        self.host: torch.Tensor | None = None
+        self.dev: torch.Tensor | None = None
+        self.frozen = False
+        # Recorded after each host-to-device copy; the host side is not rewritten before it.
+        self.copied = torch.cuda.Event()
+        self.copy_pending = False
+
+    def wait_for_copy(self) -> None:
+        if self.copy_pending:
+            self.copied.synchronize()
+            self.copy_pending = False
+
+    def reserve(self, count: int) -> None:
+        self.wait_for_copy()
+        if count <= self.capacity:
+            return
+        if self.frozen:
+            raise RuntimeError("step metadata outgrew its buffer while a CUDA graph holds it")
+        self.capacity = max(count, 2 * self.capacity, 4096)
+        self.host = torch.empty(self.capacity, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty(self.capacity, dtype=torch.int32, device=self.device)
+        self.host_np = self.host.numpy()
+
+
+@dataclass
+class _Layout:
+    """Offsets (in int32 words) of each metadata array inside the staging buffer."""
+
+    tokens: int
+    seqs: int
+    wanted: int
+    max_pages: int
+    groups: int
+
+    def __post_init__(self) -> None:
+        t, s, w = self.tokens, self.seqs, self.wanted
+        offset = 0
+
+        def take(n: int) -> int:
+            nonlocal offset
+            start = offset
+            offset += (n + 3) // 4 * 4  # keep every array 16-byte aligned
+            return start
+
+        self.token_ids = take(t)
+        self.positions = take(t)
+        self.token_seq = take(t)
+        self.seq_q_start = take(s)
+        self.seq_q_len = take(s)
+        self.seq_kv_len = take(s)
+        self.seq_slot = take(s)
+        self.logit_rows = take(w)
+        self.tables = [take(s * self.max_pages) for _ in range(self.groups)]
+        self.total = offset
+
+
+class ModelRunner:
+    def __init__(self, model: Model, cache: PagedCache, *, max_batch_tokens: int, options: dict | None = None) -> None:
+        if model.device is None:
+            raise RuntimeError("load the model's weights before building a runner")
+        self.model, self.cache = model, cache
+        self.device, self.dtype = model.device, model.dtype
+        self.lib = kernels()
+        self.max_batch_tokens = max_batch_tokens
+        self.workspace = Workspace(self.device)
+        self.staging = _Staging(self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.options = dict(options or {})
+        self.steps = 0
+        self.tokens_run = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------------------------------
+
+    def step(self, entries: Sequence[StepEntry], *, check: bool = False) -> torch.Tensor:
+        """Run one batch; returns ``[wanted, vocab]`` float32 logits on the device, in the
+        order of ``entries`` and of each entry's ``want``."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        manager = self.cache.manager
+        if not entries:
+            return torch.empty((0, self.model.head.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id} appears twice in one step")
+            seen.add(e.request_id)
+        total = sum(len(e.tokens) for e in entries)
+        if total > self.max_batch_tokens:
+            raise ValueError(f"the step holds {total} tokens, more than max_batch_tokens={self.max_batch_tokens}")
+
+        # Single decoded tokens first, then prompt portions: kernels specialised for one
+        # query per request take the front of the batch.
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        starts = [manager.length(e.request_id) for e in entries]
+        for e, start in zip(entries, starts):
+            manager.ensure(e.request_id, start + len(e.tokens))
+        self.cache.clear_new_slots()
+
+        row_of_entry = [0] * len(entries)
+        cursor = 0
+        for i in order:
+            row_of_entry[i] = cursor
+            cursor += len(entries[i].tokens)
+        wanted_rows: list[int] = []
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.request_id}: wanted place {w} is outside its {len(e.tokens)} tokens")
+                wanted_rows.append(row_of_entry[i] + int(w))
+
+        ordered = [entries[i] for i in order]
+        ordered_starts = [starts[i] for i in order]
+        ctx = self._build_context(ordered, ordered_starts, wanted_rows)
+        tables = self._tables
+        logits = self.model.forward(ctx, lambda call: self._view(call, tables))
+        for e, start in zip(entries, starts):
+            manager.advance(e.request_id, start + len(e.tokens))
+        self.steps += 1
+        self.tokens_run += total
+        if check:
+            self.check()
+        return logits
+
+    def check(self) -> None:
+        """Raise if any kernel flagged an error since the last check (synchronises)."""
+        check_error_word(self.err, "step")
+
+    # ------------------------------------------------------------------------------------------
+
+    def _view(self, call: LayerCall, tables):
+        return self.cache.view(call.cache_id, call.writes, tables)
+
+    def _build_context(self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int]) -> StepContext:
+        t = sum(len(e.tokens) for e in entries)
+        s = len(entries)
+        w = len(wanted_rows)
+        groups = len(self.cache.groups)
+        layout = _Layout(t, s, w, self.cache.max_pages_per_request, groups)
+        self.staging.reserve(layout.total)
+        buf = self.staging.host_np
+
+        def host_view(offset: int, n: int) -> np.ndarray:
+            return buf[offset : offset + n]
+
+        token_ids = host_view(layout.token_ids, t)
+        positions = host_view(layout.positions, t)
+        token_seq = host_view(layout.token_seq, t)
+        q_start = host_view(layout.seq_q_start, s)
+        q_len = host_view(layout.seq_q_len, s)
+        kv_len = host_view(layout.seq_kv_len, s)
+        slot = host_view(layout.seq_slot, s)
+        rows = host_view(layout.logit_rows, w)
+        cursor = 0
+        decode = 0
+        for i, (e, start) in enumerate(zip(entries, starts)):
+            n = len(e.tokens)
+            token_ids[cursor : cursor + n] = np.asarray(e.tokens, dtype=np.int32)
+            positions[cursor : cursor + n] = np.arange(start, start + n, dtype=np.int32)
+            token_seq[cursor : cursor + n] = i
+            q_start[i], q_len[i], kv_len[i] = cursor, n, start + n
+            slot[i] = self.cache.manager.slot(e.request_id)
+            if n == 1 and decode == i:
+                decode += 1
+            cursor += n
+        rows[:] = np.asarray(wanted_rows, dtype=np.int32)
+        ids = [e.request_id for e in entries]
+        table_views = [
+            host_view(layout.tables[g], s * layout.max_pages).reshape(s, layout.max_pages) for g in range(groups)
+        ]
+        self.cache.fill_tables(ids, table_views)
+        dev = self.staging.dev
+        dev[: layout.total].copy_(self.staging.host[: layout.total], non_blocking=True)
+        self.staging.copied.record()
+        self.staging.copy_pending = True
+
+        def dev_view(offset: int, n: int) -> torch.Tensor:
+            return dev[offset : offset + n]
+
+        self._tables = [dev_view(layout.tables[g], s * layout.max_pages).view(s, layout.max_pages) for g in range(groups)]
+        host = HostBatch(
+            token_ids=token_ids, positions=positions, token_seq=token_seq, seq_q_start=q_start,
+            seq_q_len=q_len, seq_kv_len=kv_len, seq_slot=slot, logit_rows=rows,
+        )
+        return StepContext(
+            lib=self.lib,
+            dtype=self.dtype,
+            device=self.device,
+            num_tokens=t,
+            num_seqs=s,
+            host=host,
+            token_ids=dev_view(layout.token_ids, t),
+            positions=dev_view(layout.positions, t),
+            token_seq=dev_view(layout.token_seq, t),
+            seq_q_start=dev_view(layout.seq_q_start, s),
+            seq_q_len=dev_view(layout.seq_q_len, s),
+            seq_kv_len=dev_view(layout.seq_kv_len, s),
+            seq_slot=dev_view(layout.seq_slot, s),
+            logit_rows=dev_view(layout.logit_rows, w),
+            err=self.err,
+            workspace=self.workspace,
+            num_decode_seqs=decode,
+            max_kv_len=int(kv_len.max()),
+            max_q_len=int(q_len.max()),
+            options=self.options,
+        )

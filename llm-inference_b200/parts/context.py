@@ -1,0 +1,108 @@
+"""What a part sees of one step: the batch's metadata, the cache and scratch buffers."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import numpy as np
+import torch
+
+
+@dataclass
+class HostBatch:
+    """The step's metadata as NumPy arrays on the host (the device holds the same)."""
+
+    token_ids: np.ndarray  # [T] int32
+    positions: np.ndarray  # [T] absolute position of each new token in its request
+    token_seq: np.ndarray  # [T] index of the token's request within this batch
+    seq_q_start: np.ndarray  # [S] first row of each request's run of new tokens
+    seq_q_len: np.ndarray  # [S] length of the run (1 = a decoded token)
+    seq_kv_len: np.ndarray  # [S] keys the request holds after this step
+    seq_slot: np.ndarray  # [S] state slot of each request, -1 if the cache has none
+    logit_rows: np.ndarray  # [W] rows whose logits are wanted
+
+
+@dataclass
+class CacheView:
+    """One layer call's access to the cache.
+
+    For paged keys and values: ``keys`` / ``values`` are the layer's arenas
+    ``[pages, kv_heads, page_size, head_dim]`` and ``block_table`` is ``[S, max_pages]``
+    (int32, on the device). For per-request state: ``state`` is the list of slot arrays
+    ``[slots, *shape]``. ``writes`` is false when the call only reads a cache that another
+    layer call fills.
+    """
+
+    cache_id: int
+    writes: bool = True
+    keys: torch.Tensor | None = None
+    values: torch.Tensor | None = None
+    block_table: torch.Tensor | None = None
+    num_pages: int = 0
+    max_pages: int = 0
+    page_size: int = 0
+    window: int = 0
+    state: list[torch.Tensor] | None = None
+
+
+class Workspace:
+    """Named scratch buffers that grow to the largest size asked for and are then reused."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self._flat: dict[str, torch.Tensor] = {}
+        self.frozen = False  # set while a CUDA graph that uses these buffers exists
+
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        count = 1
+        for s in shape:
+            count *= int(s)
+        key = f"{name}:{dtype}"
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < count:
+            if self.frozen and flat is not None:
+                raise RuntimeError(
+                    f"workspace buffer '{name}' would have to grow while a CUDA graph holds it"
+                )
+            flat = torch.empty(max(count, 1), dtype=dtype, device=self.device)
+            self._flat[key] = flat
+        return flat[:count].view(shape)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._flat.values())
+
+
+@dataclass
+class StepContext:
+    """Everything a part may use while the step runs."""
+
+    lib: Any  # csrc.library.KernelLibrary
+    dtype: torch.dtype
+    device: torch.device
+    num_tokens: int
+    num_seqs: int
+    host: HostBatch
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_seq: torch.Tensor
+    seq_q_start: torch.Tensor
+    seq_q_len: torch.Tensor
+    seq_kv_len: torch.Tensor
+    seq_slot: torch.Tensor
+    logit_rows: torch.Tensor
+    err: torch.Tensor  # one int32 the kernels OR error bits into
+    workspace: Workspace
+    num_decode_seqs: int = 0  # the first this-many requests of the batch feed a single token
+    max_kv_len: int = 0
+    max_q_len: int = 0
+    options: dict[str, Any] = field(default_factory=dict)
+
+    def buffer(self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None) -> torch.Tensor:
+        return self.workspace.get(name, shape, dtype or self.dtype)
+
+    @property
+    def stream(self):
+        from ctypes import c_void_p
+
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)

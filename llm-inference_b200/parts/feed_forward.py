@@ -1,0 +1,46 @@
+"""Feed-forward parts."""
+
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorSpec
+from . import ops
+from .base import Part, register_part
+from .context import StepContext
+
+
+class SwiGLU(Part):
+    """``down(silu(gate(h)) * up(h))`` without biases (python/instinct/backends/dense.py:124-128).
+    The gate and up matrices are stored as one ``[2 * intermediate, hidden]`` matrix."""
+
+    def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int) -> None:
+        self.prefix, self.hidden_size, self.intermediate_size = prefix, hidden_size, intermediate_size
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+        return [
+            TensorSpec(f"{p}gate_proj.weight", (i, h)),
+            TensorSpec(f"{p}up_proj.weight", (i, h)),
+            TensorSpec(f"{p}down_proj.weight", (h, i)),
+        ]
+
+    def load(self, tensors, dtype, device) -> None:
+        p = self.prefix
+        self.w_gate_up = torch.cat(
+            [tensors[f"{p}{n}.weight"].to(device=device, dtype=dtype) for n in ("gate_proj", "up_proj")]
+        ).contiguous()
+        self.w_down = tensors[f"{p}down_proj.weight"].to(device=device, dtype=dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        t, i = ctx.num_tokens, self.intermediate_size
+        gate_up = ops.linear(ctx, h, self.w_gate_up, ctx.buffer("gate_up", (t, 2 * i)))
+        act = ops.silu_mul(ctx, gate_up, ctx.buffer("act", (t, i)))
+        return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,44 @@
+"""Normalisation parts."""
+
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorSpec
+from . import ops
+from .base import Part, register_part
+from .context import StepContext
+
+
+class RMSNorm(Part):
+    """``y = v * rsqrt(mean(v^2) + eps) * weight`` with ``v = x + delta``, all in 32-bit
+    (python/instinct/backends/portable.py:144-149). The add into the residual stream is
+    part of the same kernel."""
+
+    def __init__(self, *, name: str, hidden_size: int, eps: float) -> None:
+        self.name, self.hidden_size, self.eps = name, hidden_size, float(eps)
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name + ".weight", (self.hidden_size,), init="one_plus_normal")]
+
+    def load(self, tensors, dtype, device) -> None:
+        self.weight = tensors[self.name + ".weight"].to(device=device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * 4
+
+    def forward(
+        self,
+        ctx: StepContext,
+        x: torch.Tensor,
+        delta: torch.Tensor | None,
+        rows: torch.Tensor | None = None,
+        out_name: str = "normed",
+    ) -> torch.Tensor:
+        count = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (count, self.hidden_size))
+        return ops.rmsnorm(ctx, x, delta, self.weight, self.eps, out, rows)
+
+
+register_part("norm", "rmsnorm", RMSNorm)

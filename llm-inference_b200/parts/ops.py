@@ -1,0 +1,192 @@
+"""Tensor-level calls into the kernel library (and the library matrix product).
+
+Each function checks shapes and strides, then launches on the current CUDA stream. Matrix
+products in bfloat16 go to the vendor library through ``torch.mm``, as the reference sends
+its linear layers to cuBLASLt (cuda/execution_context.cu:95-110); in float32 they use this
+engine's own FMA kernel so that nothing runs in a reduced-precision matrix mode.
+"""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_int64
+
+import torch
+
+from ..csrc.library import KernelError, dtype_code, ptr
+from .context import CacheView, StepContext
+
+
+def _need(cond: bool, message: str) -> None:
+    if not cond:
+        raise KernelError(message)
+
+
+_MM_OUT_DTYPE: bool | None = None
+
+
+def _mm_f32_out(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """bf16 x bf16 -> fp32 through the library, accumulating and storing in 32-bit."""
+    global _MM_OUT_DTYPE
+    if _MM_OUT_DTYPE is None:
+        try:
+            a = torch.zeros(8, 16, dtype=torch.bfloat16, device=x.device)
+            torch.mm(a, a.t(), out_dtype=torch.float32)
+            _MM_OUT_DTYPE = True
+        except (TypeError, RuntimeError):
+            _MM_OUT_DTYPE = False
+    if _MM_OUT_DTYPE:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    else:
+        out.copy_(torch.mm(x, weight.t()))
+
+
+def linear(
+    ctx: StepContext,
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    bias: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``out = x @ weight.T (+ bias)``; ``weight`` is ``[out_features, in_features]``."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(weight.shape[1] == k, f"linear: x is [{m},{k}] but weight is {list(weight.shape)}")
+    _need(tuple(out.shape) == (m, n), f"linear: out is {list(out.shape)}, expected [{m},{n}]")
+    _need(x.is_contiguous() and weight.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
+    if m == 0:
+        return out
+    if x.dtype == torch.float32:
+        _need(weight.dtype == torch.float32 and out.dtype == torch.float32, "linear: float32 path needs float32 operands")
+        _need(bias is None or bias.dtype == torch.float32, "linear: bias must be float32")
+        ctx.lib.call(
+            "b200_gemm_f32", ptr(x), ptr(weight), ptr(bias), ptr(out), c_int(m), c_int(n), c_int(k),
+            c_int(k), c_int(k), c_int(n), ctx.stream,
+        )
+        return out
+    _need(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: bfloat16 path needs bfloat16 operands")
+    if out.dtype == torch.float32:
+        _need(bias is None, "linear: no bias on the 32-bit output path")
+        _mm_f32_out(x, weight, out)
+    elif bias is not None:
+        torch.addmm(bias, x, weight.t(), out=out)
+    else:
+        torch.mm(x, weight.t(), out=out)
+    return out
+
+
+def embedding_gather(ctx: StepContext, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    vocab, hidden = table.shape
+    _need(tuple(out.shape) == (ctx.num_tokens, hidden) and out.dtype == torch.float32, "embedding: bad output")
+    ctx.lib.call(
+        "b200_embedding_gather", ptr(table), c_int(dtype_code(table.dtype)), ptr(ctx.token_ids), ptr(out),
+        c_int(ctx.num_tokens), c_int(hidden), c_int(vocab), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+def rmsnorm(
+    ctx: StepContext,
+    x: torch.Tensor,
+    delta: torch.Tensor | None,
+    weight: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    rows: torch.Tensor | None = None,
+) -> torch.Tensor:
+    hidden = x.shape[1]
+    num_rows = x.shape[0] if rows is None else rows.shape[0]
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "rmsnorm: the residual stream is contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.shape == (hidden,), "rmsnorm: weight must be float32 [hidden]")
+    _need(tuple(out.shape) == (num_rows, hidden) and out.is_contiguous(), "rmsnorm: bad output shape")
+    _need(delta is None or (delta.shape == x.shape and delta.dtype == out.dtype and delta.is_contiguous()), "rmsnorm: bad delta")
+    ctx.lib.call(
+        "b200_rmsnorm", ptr(x), ptr(delta), ptr(weight), ptr(out), ptr(rows), c_int(num_rows), c_int(hidden),
+        c_float(eps), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def silu_mul(ctx: StepContext, gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    tokens, twice = gate_up.shape
+    inter = twice // 2
+    _need(twice == 2 * inter and tuple(out.shape) == (tokens, inter), "silu_mul: bad shapes")
+    _need(gate_up.is_contiguous() and out.is_contiguous() and gate_up.dtype == out.dtype, "silu_mul: bad operands")
+    ctx.lib.call(
+        "b200_silu_mul", ptr(gate_up), ptr(out), c_int(tokens), c_int(inter), c_int(dtype_code(out.dtype)), ctx.stream,
+    )
+    return out
+
+
+def rope_kv_write(
+    ctx: StepContext,
+    cache: CacheView,
+    qkv: torch.Tensor,
+    bias: torch.Tensor | None,
+    inv_freq: torch.Tensor,
+    q_out: torch.Tensor,
+    q_heads: int,
+    kv_heads: int,
+    head_dim: int,
+) -> torch.Tensor:
+    tokens = qkv.shape[0]
+    width = (q_heads + 2 * kv_heads) * head_dim
+    rot = 2 * inv_freq.numel()
+    _need(tuple(qkv.shape) == (tokens, width) and qkv.is_contiguous(), "rope_kv_write: bad qkv")
+    _need(tuple(q_out.shape) == (tokens, q_heads * head_dim) and q_out.is_contiguous(), "rope_kv_write: bad q_out")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "rope_kv_write: bias must be float32 [width]")
+    _need(inv_freq.dtype == torch.float32, "rope_kv_write: inverse frequencies must be float32")
+    _need(cache.keys.dtype == qkv.dtype and cache.values.dtype == qkv.dtype, "rope_kv_write: cache dtype differs")
+    ctx.lib.call(
+        "b200_rope_kv_write", ptr(qkv), ptr(bias), ptr(inv_freq), ptr(ctx.positions), ptr(ctx.token_seq),
+        ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages), ptr(cache.keys), ptr(cache.values),
+        ptr(q_out), c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(rot),
+        c_int(cache.page_size), c_int(1 if cache.writes else 0), c_int(dtype_code(qkv.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return q_out
+
+
+def paged_attention_plain(
+    ctx: StepContext,
+    cache: CacheView,
+    q: torch.Tensor,
+    out: torch.Tensor,
+    q_heads: int,
+    kv_heads: int,
+    head_dim: int,
+    scale: float,
+    *,
+    first_token: int = 0,
+    num_tokens: int | None = None,
+) -> torch.Tensor:
+    """Attention of rows ``first_token .. first_token + num_tokens`` of the step over the cache."""
+    tokens = ctx.num_tokens - first_token if num_tokens is None else num_tokens
+    if tokens <= 0:
+        return out
+    _need(q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype, "attention: bad operands")
+    _need(cache.keys.dtype == q.dtype, "attention: cache dtype differs from the queries'")
+    row_bytes = q_heads * head_dim * q.element_size()
+    ctx.lib.call(
+        "b200_paged_attention_plain",
+        ptr(q) if first_token == 0 else _offset(q, first_token * row_bytes),
+        ptr(cache.keys), ptr(cache.values),
+        _offset(ctx.positions, first_token * 4), _offset(ctx.token_seq, first_token * 4),
+        ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
+        ptr(out) if first_token == 0 else _offset(out, first_token * row_bytes),
+        c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size),
+        c_int(cache.window), c_float(scale), c_int(dtype_code(q.dtype)), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
+def _offset(tensor: torch.Tensor, nbytes: int):
+    from ctypes import c_void_p
+
+    return c_void_p(tensor.data_ptr() + nbytes)
+
+
+def argmax_rows(lib, logits: torch.Tensor, out: torch.Tensor, row_index: torch.Tensor | None, rows: int, stream) -> None:
+    _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "argmax: logits must be float32 rows")
+    lib.call(
+        "b200_argmax_rows", ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)),
+        ptr(row_index), ptr(out), stream,
+    )

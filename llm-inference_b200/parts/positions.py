@@ -1,0 +1,34 @@
+"""Position encodings."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .base import Part, register_part
+
+
+class RotaryEncoding(Part):
+    """Rotary position encoding over the first ``rotary_dims`` dims of each head, pairing
+    dim i with i + rotary_dims / 2; inverse frequencies ``theta ** (-2 i / rotary_dims)`` are
+    tabulated once in 32-bit and the kernel multiplies them by the position
+    (python/instinct/backends/portable.py:115-132)."""
+
+    def __init__(self, *, head_dim: int, theta: float, rotary_dims: int | None = None) -> None:
+        self.head_dim = head_dim
+        self.rotary_dims = head_dim if rotary_dims is None else rotary_dims
+        if self.rotary_dims % 2 or not 0 <= self.rotary_dims <= head_dim:
+            raise ValueError(f"rotary_dims={self.rotary_dims} must be even and at most head_dim={head_dim}")
+        self.theta = float(theta)
+        self.inv_freq: torch.Tensor | None = None
+
+    def table(self) -> np.ndarray:
+        half = self.rotary_dims // 2
+        exponent = -(np.arange(half, dtype=np.float32) * np.float32(2.0) / np.float32(self.rotary_dims))
+        return np.power(np.float32(self.theta), exponent, dtype=np.float32)
+
+    def load(self, tensors, dtype, device) -> None:
+        self.inv_freq = torch.from_numpy(self.table()).to(device)
+
+
+register_part("position", "rotary", RotaryEncoding)

@@ -1,0 +1,3 @@
+from .params import GREEDY, SamplingParams
+
+__all__ = ["GREEDY", "SamplingParams"]

@@ -1,0 +1,136 @@
+"""Replay through bin/trace_run against the plain implementation, every way of cutting the work."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from helpers import PAGE_SIZE, TINY, TOLERANCE, make_model_folder, plain_weights, random_tokens, run_trace
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 100], "B": [1, 23, 40, 70, 150]}
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request, tmp_path_factory):
+    name = request.param
+    folder = make_model_folder(tmp_path_factory.mktemp(f"tiny{name}"), TINY[name], seed=11 + ord(name))
+    config, weights = plain_weights(folder)
+    rng = np.random.default_rng(5)
+    sequences = {f"r{i}": random_tokens(rng, config["vocab_size"], n) for i, n in enumerate(LENGTHS[name])}
+    expected = {key: plain.forward(config, weights, tokens) for key, tokens in sequences.items()}
+    return name, folder, sequences, expected
+
+
+def compare(got: np.ndarray, want: np.ndarray, dtype: str, what: str) -> None:
+    error = np.abs(got.astype(np.float64) - want)
+    worst = np.unravel_index(np.argmax(error), error.shape)
+    assert error.max() <= TOLERANCE[dtype], f"{what}: max |logit error| {error.max():.3e} at row {worst[0]}, token {worst[1]}"
+
+
+def pool_for(lengths) -> int:
+    return sum((n + 63) // 64 * 64 for n in lengths)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompt_alone(tiny, dtype, tmp_path):
+    name, folder, sequences, expected = tiny
+    for key, tokens in sequences.items():
+        steps = [{"step": 0, "entries": [{"id": key, "tokens": tokens, "want": list(range(len(tokens)))}], "end": [key]}]
+        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
+        compare(logits[0], expected[key], dtype, f"{name}/{key} whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_32_tokens_one_by_one(tiny, dtype, tmp_path):
+    name, folder, sequences, expected = tiny
+    for key, tokens in sequences.items():
+        head = max(0, len(tokens) - 32)
+        steps, rows = [], []
+        if head:
+            steps.append({"step": 0, "entries": [{"id": key, "tokens": tokens[:head], "want": [head - 1]}], "end": []})
+            rows.append(head - 1)
+        for position in range(head, len(tokens)):
+            steps.append({"step": len(steps), "entries": [{"id": key, "tokens": [tokens[position]], "want": [0]}], "end": []})
+            rows.append(position)
+        steps[-1]["end"] = [key]
+        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
+        got = np.concatenate([logits[s["step"]] for s in steps])
+        compare(got, expected[key][rows], dtype, f"{name}/{key} decode tail")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_portions_of_changing_size(tiny, dtype, tmp_path):
+    name, folder, sequences, expected = tiny
+    sizes = [7, 2, 5, 3, 2, 16, 2, 9, 4, 2, 31, 2]
+    for key, tokens in sequences.items():
+        steps, rows, at, turn = [], [], 0, 0
+        while at < len(tokens):
+            n = min(sizes[turn % len(sizes)], len(tokens) - at)
+            if len(tokens) - at - n == 1:  # never leave a portion below two tokens by accident
+                n += 1
+            want = [0, n - 1] if n > 1 else [0]
+            steps.append({"step": len(steps), "entries": [{"id": key, "tokens": tokens[at : at + n], "want": want}], "end": []})
+            rows += [at + w for w in want]
+            at += n
+            turn += 1
+        steps[-1]["end"] = [key]
+        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
+        got = np.concatenate([logits[s["step"]] for s in steps])
+        compare(got, expected[key][rows], dtype, f"{name}/{key} portions")
+
+
+def mixed_trace(sequences: dict[str, list[int]], live_limit: int = 4):
+    """Up to four live requests: staggered starts, portions of some beside single tokens of
+    others; finished requests leave so that their pages are used again by later ones."""
+    keys = list(sequences)
+    cursor = {k: 0 for k in keys}
+    portion = {k: [5, 2, 11, 3][i % 4] for i, k in enumerate(keys)}
+    waiting = list(keys) + [k + "'" for k in keys]  # every sequence runs twice
+    tokens_of = {**sequences, **{k + "'": v for k, v in sequences.items()}}
+    cursor.update({k + "'": 0 for k in keys})
+    portion.update({k + "'": [3, 13, 2, 7][i % 4] for i, k in enumerate(keys)})
+    live: list[str] = []
+    steps, rows = [], []
+    step = 0
+    while waiting or live:
+        if waiting and len(live) < live_limit and step % 2 == 0:
+            live.append(waiting.pop(0))
+        entries, ended = [], []
+        for k in list(live):
+            if (step + len(k)) % 5 == 4 and len(live) > 1:
+                continue  # this request sits the step out
+            tokens = tokens_of[k]
+            remaining = len(tokens) - cursor[k]
+            # Prompt portions first; the last six tokens go one by one, like decoded tokens.
+            n = 1 if remaining <= 6 else max(1, min(portion[k], remaining - 6))
+            want = [n - 1]
+            entries.append({"id": k, "tokens": tokens[cursor[k] : cursor[k] + n], "want": want})
+            rows.append((k.rstrip("'"), cursor[k] + n - 1))
+            cursor[k] += n
+            if cursor[k] == len(tokens):
+                ended.append(k)
+                live.remove(k)
+        if entries or ended:
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+        step += 1
+    return steps, rows
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_with_page_reuse(tiny, dtype, tmp_path):
+    name, folder, sequences, expected = tiny
+    steps, rows = mixed_trace(sequences)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if len(s["entries"]) > 1)
+    # Room for the four longest at once: far less than all requests together, so pages of
+    # finished requests must be handed out again.
+    longest = sorted((len(t) for t in sequences.values()), reverse=True)
+    pool = pool_for((longest * 2)[:4])
+    assert pool < pool_for([len(t) for t in sequences.values()] * 2)
+    logits = run_trace(folder, dtype, steps, tmp_path / "mixed", pool, PAGE_SIZE[name])
+    got = np.concatenate([logits[s["step"]] for s in steps if s["step"] in logits])
+    want = np.stack([expected[k][row] for k, row in rows])
+    compare(got, want, dtype, f"{name} mixed")
