@@ -201,17 +201,20 @@ class Qwen2Config(ModelConfig):
             unknown = set(self.layer_types) - {"full_attention", "sliding_attention"}
             if unknown:
                 raise ConfigError(f"unknown layer types {sorted(unknown)}")
-        if any(self.layer_window(i) for i in range(self.num_hidden_layers)):
+        if any(self.layer_is_windowed(i) for i in range(self.num_hidden_layers)):
             if self.sliding_window <= 0:
                 raise ConfigError("sliding-window layers need a positive sliding_window")
+        if self.sliding_window < 0 or self.max_window_layers < 0:
+            raise ConfigError("sliding_window and max_window_layers cannot be negative")
+
+    def layer_is_windowed(self, layer: int) -> bool:
+        if self.layer_types:
+            return self.layer_types[layer] == "sliding_attention"
+        return self.use_sliding_window and layer >= self.max_window_layers
 
     def layer_window(self, layer: int) -> int:
         """Window of ``layer`` in positions (the query's own included), 0 = all keys."""
-        if self.layer_types:
-            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else 0
-        if self.use_sliding_window and layer >= self.max_window_layers:
-            return self.sliding_window
-        return 0
+        return self.sliding_window if self.layer_is_windowed(layer) else 0
 
     def to_json_dict(self) -> dict[str, Any]:
         out: dict[str, Any] = {

@@ -35,13 +35,14 @@ def parse_dtype(dtype: str | torch.dtype) -> torch.dtype:
 
 def load_model(model_path: str | Path, dtype: str | torch.dtype = "bfloat16", device: str | torch.device = "cuda:0") -> Model:
     """Build the model that ``config.json`` names and load its safetensors weights."""
+    compute_dtype = parse_dtype(dtype)
     folder = Path(model_path)
     if not folder.is_dir():
         raise FileNotFoundError(f"{folder} is not a model folder (config.json plus *.safetensors)")
     entry, config = parse_config(read_config_json(folder))
     model = Model(entry.recipe(config))
     tensors = load_weights(folder, model.tensor_specs(), device="cpu")
-    model.load(tensors, parse_dtype(dtype), torch.device(device))
+    model.load(tensors, compute_dtype, torch.device(device))
     return model
 
 

@@ -1,0 +1,399 @@
+"""Each kernel alone against a plain PyTorch float32 (or float64) reference of the same op,
+at sizes other than the engine's."""
+
+from __future__ import annotations
+
+import math
+from ctypes import c_float, c_int, c_int64, c_void_p
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from llm_inference_b200.csrc.library import kernels
+
+    return kernels()
+
+
+def make_ctx(lib, token_ids=None, positions=None, token_seq=None):
+    from llm_inference_b200.parts.context import Workspace
+
+    dev = torch.device("cuda:0")
+    n = len(positions) if positions is not None else len(token_ids)
+    as_dev = lambda v: torch.tensor(v, dtype=torch.int32, device=dev) if v is not None else None
+    return SimpleNamespace(
+        lib=lib,
+        device=dev,
+        num_tokens=n,
+        token_ids=as_dev(token_ids),
+        positions=as_dev(positions),
+        token_seq=as_dev(token_seq),
+        err=torch.zeros(1, dtype=torch.int32, device=dev),
+        stream=c_void_p(torch.cuda.current_stream().cuda_stream),
+        workspace=Workspace(dev),
+    )
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_gather(lib, dtype):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(0)
+    table = torch.randn(1000, 200, device="cuda").to(dtype)
+    ids = [0, 999, 5, 5, 123, 77, 998]
+    ctx = make_ctx(lib, token_ids=ids)
+    out = torch.empty(len(ids), 200, device="cuda")
+    ops.embedding_gather(ctx, table, out)
+    assert torch.equal(out, table[ids].float())
+    assert int(ctx.err.item()) == 0
+    # An id outside the table is reported, not read.
+    ctx = make_ctx(lib, token_ids=[3, 1000])
+    ops.embedding_gather(ctx, table, out[:2])
+    assert int(ctx.err.item()) == 2 and torch.all(out[1] == 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [1000, 96, 4104])
+def test_rmsnorm_with_and_without_the_residual_add(lib, dtype, hidden):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(1)
+    rows, eps = 37, 1e-5
+    x = torch.randn(rows, hidden, device="cuda") * 3
+    delta = torch.randn(rows, hidden, device="cuda").to(dtype)
+    weight = 1 + 0.1 * torch.randn(hidden, device="cuda")
+    ctx = make_ctx(lib, positions=[0] * rows)
+
+    def reference(v):
+        v = v.double()
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * weight.double()
+
+    out = torch.empty(rows, hidden, device="cuda", dtype=dtype)
+    x0 = x.clone()
+    ops.rmsnorm(ctx, x0, None, weight, eps, out)
+    assert torch.equal(x0, x)
+    torch.testing.assert_close(out.double(), reference(x), **tol(dtype))
+    x1 = x.clone()
+    ops.rmsnorm(ctx, x1, delta, weight, eps, out)
+    torch.testing.assert_close(x1, x + delta.float(), atol=1e-6, rtol=1e-6)  # the sum stays 32-bit
+    torch.testing.assert_close(out.double(), reference(x + delta.float()), **tol(dtype))
+    # Only some rows, and the stream is left alone.
+    picks = torch.tensor([36, 0, 5, 5], dtype=torch.int32, device="cuda")
+    x2 = x.clone()
+    some = torch.empty(4, hidden, device="cuda", dtype=dtype)
+    ops.rmsnorm(ctx, x2, delta, weight, eps, some, picks)
+    assert torch.equal(x2, x)
+    torch.testing.assert_close(some.double(), reference(x + delta.float())[picks.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(37, 83, 129), (1, 311, 96), (130, 64, 64), (5, 7, 3), (64, 152, 1000)])
+def test_gemm_f32_is_true_32_bit(lib, m, n, k):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(2)
+    # Values that TF32 or bfloat16 products would visibly corrupt.
+    a = torch.randn(m, k, device="cuda") * (1 + 1e-4 * torch.randn(m, k, device="cuda"))
+    w = torch.randn(n, k, device="cuda")
+    bias = torch.randn(n, device="cuda")
+    ctx = make_ctx(lib, positions=[0] * m)
+    out = torch.empty(m, n, device="cuda")
+    ops.linear(ctx, a, w, out, bias)
+    want = (a.double() @ w.double().T + bias.double())
+    error = (out.double() - want).abs().max().item()
+    assert error < 2e-5 * math.sqrt(k), error
+    # A row's result does not depend on the other rows of the call.
+    alone = torch.empty(1, n, device="cuda")
+    ops.linear(ctx, a[m // 2 : m // 2 + 1].contiguous(), w, alone, bias)
+    assert torch.equal(alone[0], out[m // 2])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(lib, dtype):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(3)
+    gate_up = (torch.randn(13, 2 * 272, device="cuda") * 4).to(dtype)
+    out = torch.empty(13, 272, device="cuda", dtype=dtype)
+    ops.silu_mul(make_ctx(lib, positions=[0] * 13), gate_up, out)
+    g, u = gate_up[:, :272].double(), gate_up[:, 272:].double()
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+def paged_layout(seq_lens, page_size, extra_pages=3, seed=0):
+    """Random, non-contiguous page assignment; returns (tables [S, max_pages], num_pages)."""
+    rng = np.random.default_rng(seed)
+    need = [math.ceil(n / page_size) for n in seq_lens]
+    num_pages = sum(need) + extra_pages
+    order = rng.permutation(num_pages)
+    max_pages = max(need) + 1
+    tables = np.full((len(seq_lens), max_pages), -1, dtype=np.int32)
+    at = 0
+    for s, count in enumerate(need):
+        tables[s, :count] = order[at : at + count]
+        at += count
+    return tables, num_pages
+
+
+def gather_cache(arena, table, length, page_size):
+    """[length, kv_heads, head_dim] of one request from an arena [pages, kv_heads, page, dim]."""
+    rows = []
+    for pos in range(length):
+        rows.append(arena[int(table[pos // page_size]), :, pos % page_size, :])
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("q_heads,kv_heads,head_dim,rot,page", [(4, 2, 16, 16, 4), (6, 1, 48, 32, 8), (5, 5, 128, 128, 16)])
+def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page):
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.context import CacheView
+
+    torch.manual_seed(4)
+    starts, runs = [37, 0, 5], [1, 9, 3]  # a decoded token, a fresh prompt, a later portion
+    seq_lens = [s + r for s, r in zip(starts, runs)]
+    tables, num_pages = paged_layout(seq_lens, page)
+    positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
+    token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
+    t = len(positions)
+    width = (q_heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(t, width, device="cuda").to(dtype)
+    bias = torch.randn(width, device="cuda") * 0.5
+    theta = 1e6
+    inv_freq = torch.from_numpy(plain.rope_inverse_frequencies(rot, theta)).cuda()
+    keys = torch.full((num_pages, kv_heads, page, head_dim), 7.0, device="cuda", dtype=dtype)
+    values = keys.clone()
+    q_out = torch.empty(t, q_heads * head_dim, device="cuda", dtype=dtype)
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq)
+    table_dev = torch.from_numpy(tables).cuda()
+    view = CacheView(0, True, keys, values, table_dev, num_pages, tables.shape[1], page)
+    ops.rope_kv_write(ctx, view, qkv, bias, inv_freq, q_out, q_heads, kv_heads, head_dim)
+    assert int(ctx.err.item()) == 0
+
+    full = qkv.double().cpu().numpy() + bias.double().cpu().numpy()
+    q = full[:, : q_heads * head_dim].reshape(t, q_heads, head_dim)
+    k = full[:, q_heads * head_dim : (q_heads + kv_heads) * head_dim].reshape(t, kv_heads, head_dim)
+    v = full[:, (q_heads + kv_heads) * head_dim :].reshape(t, kv_heads, head_dim)
+
+    def rotate(x):
+        out = x.copy()
+        out[..., :rot] = plain.rope(x[..., :rot], positions, theta)
+        return out
+
+    kw = tol(dtype)
+    np.testing.assert_allclose(q_out.double().cpu().numpy().reshape(t, q_heads, head_dim), rotate(q), **kw)
+    k_rot = rotate(k)
+    touched = torch.zeros(num_pages, page, dtype=torch.bool)
+    for row, (pos, s) in enumerate(zip(positions, token_seq)):
+        pg, r = int(tables[s, pos // page]), pos % page
+        touched[pg, r] = True
+        np.testing.assert_allclose(keys[pg, :, r].double().cpu().numpy(), k_rot[row], **kw)
+        np.testing.assert_allclose(values[pg, :, r].double().cpu().numpy(), v[row], **kw)
+    # Nothing else in the arena was written.
+    untouched = ~touched
+    assert torch.all(keys.float().cpu().permute(0, 2, 1, 3)[untouched] == 7.0)
+    assert torch.all(values.float().cpu().permute(0, 2, 1, 3)[untouched] == 7.0)
+    # A call that only reads another layer's cache rotates the queries and writes nothing.
+    before = keys.clone()
+    view.writes = False
+    ops.rope_kv_write(ctx, view, qkv, bias, inv_freq, q_out, q_heads, kv_heads, head_dim)
+    assert torch.equal(keys, before)
+    # A table entry that is not a page is reported.
+    bad = table_dev.clone()
+    bad[1, 0] = -1
+    view = CacheView(0, True, keys, values, bad, num_pages, tables.shape[1], page)
+    ops.rope_kv_write(ctx, view, qkv, bias, inv_freq, q_out, q_heads, kv_heads, head_dim)
+    assert int(ctx.err.item()) & 1
+
+
+def dense_attention(q, k, v, scale, window, start):
+    """q [n, heads, d] at positions start..start+n-1 over k, v [start+n, kv_heads, d], float64."""
+    n, heads, d = q.shape
+    groups = heads // k.shape[1]
+    k = k.repeat_interleave(groups, dim=1).permute(1, 0, 2)
+    v = v.repeat_interleave(groups, dim=1).permute(1, 0, 2)
+    scores = (q.permute(1, 0, 2) * scale) @ k.transpose(1, 2)
+    query = torch.arange(start, start + n, device=q.device)[:, None]
+    key = torch.arange(k.shape[1], device=q.device)[None, :]
+    mask = key <= query
+    if window:
+        mask &= key > query - window
+    scores = scores.masked_fill(~mask[None], float("-inf"))
+    return (torch.softmax(scores, -1) @ v).permute(1, 0, 2).reshape(n, heads * d)
+
+
+def attention_case(dtype, q_heads, kv_heads, head_dim, page, window, starts, runs, seed=5, spike=None):
+    torch.manual_seed(seed)
+    seq_lens = [s + r for s, r in zip(starts, runs)]
+    tables, num_pages = paged_layout(seq_lens, page, seed=seed)
+    keys = torch.randn(num_pages, kv_heads, page, head_dim, device="cuda").to(dtype)
+    values = torch.randn(num_pages, kv_heads, page, head_dim, device="cuda").to(dtype)
+    positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
+    token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
+    t = len(positions)
+    q = torch.randn(t, q_heads, head_dim, device="cuda").to(dtype)
+    if spike is not None:
+        # One far key lines up with one query so that a single score dominates its row: a
+        # wrong page or row for that key cannot hide in the average.
+        seq, key_pos, row = spike
+        pg, r = int(tables[seq, key_pos // page]), key_pos % page
+        direction = torch.randn(head_dim, device="cuda")
+        direction = direction / direction.norm() * 6
+        keys[pg, :, r, :] = direction.to(dtype)
+        q[row] = (direction * 3).to(dtype)
+        values[pg, :, r, :] = 10.0
+    expected = []
+    row = 0
+    for s, (start, run) in enumerate(zip(starts, runs)):
+        k = gather_cache(keys, tables[s], start + run, page).double()
+        v = gather_cache(values, tables[s], start + run, page).double()
+        expected.append(dense_attention(q[row : row + run].double(), k, v, head_dim**-0.5, window, start))
+        row += run
+    return q.reshape(t, -1).contiguous(), keys, values, tables, num_pages, positions, token_seq, torch.cat(expected)
+
+
+CASES = [
+    # q_heads, kv_heads, head_dim, page, window, starts, runs
+    (4, 2, 16, 4, 0, [0, 40, 7], [9, 1, 5]),
+    (6, 1, 32, 8, 24, [0, 100, 23, 24], [30, 1, 2, 1]),
+    (12, 2, 128, 16, 0, [300, 0], [1, 70]),
+    (5, 5, 48, 64, 0, [129, 63], [3, 2]),
+    (8, 4, 256, 16, 10, [50, 0], [1, 33]),
+    (3, 3, 80, 32, 0, [1000], [1]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", CASES)
+def test_paged_attention_plain(lib, dtype, case):
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.context import CacheView
+
+    q_heads, kv_heads, head_dim, page, window, starts, runs = case
+    q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+        dtype, q_heads, kv_heads, head_dim, page, window, starts, runs
+    )
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq)
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+    out = torch.empty_like(q)
+    ops.paged_attention_plain(ctx, view, q, out, q_heads, kv_heads, head_dim, head_dim**-0.5)
+    assert int(ctx.err.item()) == 0
+    torch.testing.assert_close(out.double(), expected, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(lib, dtype):
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.context import CacheView
+
+    q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+        dtype, 4, 2, 64, 16, 0, [700, 0], [1, 4], spike=(0, 17, 0)
+    )
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq)
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], 16)
+    out = torch.empty_like(q)
+    ops.paged_attention_plain(ctx, view, q, out, 4, 2, 64, 64**-0.5)
+    assert expected[0].abs().min() > 9.0  # the spike's value dominates the reference row
+    torch.testing.assert_close(out.double(), expected, **tol(dtype))
+
+
+def test_window_edge_is_exact(lib):
+    """The key at position - window must be invisible and the one at position - window + 1 visible."""
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.context import CacheView
+
+    head_dim, page, window, pos = 32, 8, 24, 60
+    tables, num_pages = paged_layout([pos + 1], page)
+    keys = torch.zeros(num_pages, 1, page, head_dim, device="cuda")
+    values = torch.zeros(num_pages, 1, page, head_dim, device="cuda")
+    for p in range(pos + 1):
+        values[int(tables[0, p // page]), 0, p % page, 0] = float(p)
+    q = torch.zeros(1, head_dim, device="cuda")
+    ctx = make_ctx(lib, positions=[pos], token_seq=[0])
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+    out = torch.empty_like(q)
+    ops.paged_attention_plain(ctx, view, q, out, 1, 1, head_dim, 1.0)
+    visible = list(range(pos - window + 1, pos + 1))
+    assert abs(out[0, 0].item() - sum(visible) / len(visible)) < 1e-4
+
+
+def test_argmax_rows_takes_the_lowest_index_on_ties(lib):
+    logits = torch.randn(6, 1511, device="cuda")
+    logits[0, 700] = logits[0, 33] = 50.0
+    logits[1, 1510] = 60.0
+    logits[2, 0] = 60.0
+    logits[3] = 0.0
+    out = torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    s = c_void_p(torch.cuda.current_stream().cuda_stream)
+    lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(6), c_int(1511), c_int64(1511), c_void_p(0), c_void_p(out.data_ptr()), s)
+    want = logits.argmax(-1).tolist()
+    want[0], want[3] = 33, 0
+    assert out.tolist() == want
+    # Only some rows.
+    rows = torch.tensor([4, 1], dtype=torch.int32, device="cuda")
+    out.fill_(-1)
+    lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(2), c_int(1511), c_int64(1511), c_void_p(rows.data_ptr()), c_void_p(out.data_ptr()), s)
+    assert out.tolist() == [-1, 1510, -1, -1, want[4], -1]
+
+
+def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys):
+    rows, vocab = logits.shape
+    f = lambda v: torch.tensor(v, dtype=torch.float32, device="cuda")
+    t, p, m = f(temperature), f(top_p), f(min_p)
+    k = torch.tensor(top_k, dtype=torch.int32, device="cuda")
+    key = torch.tensor(np.asarray(keys, dtype=np.uint64).view(np.int64), dtype=torch.int64, device="cuda")
+    out = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    lib.call(
+        "b200_sample_rows", c_void_p(logits.data_ptr()), c_int(rows), c_int(vocab), c_int64(logits.stride(0)),
+        c_void_p(t.data_ptr()), c_void_p(p.data_ptr()), c_void_p(m.data_ptr()), c_void_p(k.data_ptr()),
+        c_void_p(key.data_ptr()), c_void_p(0), c_void_p(out.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream),
+    )
+    return out.tolist()
+
+
+@pytest.mark.parametrize(
+    "vocab,settings",
+    [
+        (311, dict(temperature=0.8)),
+        (311, dict(temperature=1.3, top_k=7)),
+        (311, dict(temperature=0.9, top_p=0.7)),
+        (311, dict(temperature=1.0, min_p=0.15)),
+        (5000, dict(temperature=1.0)),  # more tokens than candidates: only the top 1024 may be drawn
+        (5000, dict(temperature=0.7, top_k=40, top_p=0.9, min_p=0.02)),
+    ],
+)
+def test_sampling_matches_the_plain_filters_and_draw(lib, vocab, settings):
+    rng = np.random.default_rng(vocab)
+    base = torch.from_numpy(rng.normal(0, 2.0, vocab).astype(np.float32)).cuda()
+    draws = 400
+    logits = base.repeat(draws, 1).contiguous()
+    keys = [plain.draw_key(99, i) for i in range(draws)]
+    temperature = settings.get("temperature", 1.0)
+    top_k, top_p, min_p = settings.get("top_k", 0), settings.get("top_p", 1.0), settings.get("min_p", 0.0)
+    got = run_sampler(lib, logits, [temperature] * draws, [top_p] * draws, [min_p] * draws, [top_k] * draws, keys)
+    probs = plain.surviving_probabilities(base.cpu().numpy(), temperature, top_k, top_p, min_p)
+    assert all(probs[t] > 0 for t in got), "a filtered token was drawn"
+    # The engine draws by inverse CDF in token order with u = uniform_from_key(key).
+    cdf = np.cumsum(probs)
+    agree = 0
+    for token, key in zip(got, keys):
+        u = plain.uniform_from_key(key)
+        expected = int(np.searchsorted(cdf, u * cdf[-1], side="right"))
+        agree += token == expected
+    assert agree >= draws - 2, f"only {agree} of {draws} draws match the plain inverse CDF"
+    # Same key, same token; and the result does not depend on the row it sits in.
+    again = run_sampler(lib, logits[:3], [temperature] * 3, [top_p] * 3, [min_p] * 3, [top_k] * 3, [keys[7], keys[7], keys[0]])
+    assert again[0] == again[1] == got[7] and again[2] == got[0]

@@ -34,52 +34,73 @@ def pool_for(lengths) -> int:
     return sum((n + 63) // 64 * 64 for n in lengths)
 
 
+def run_one_after_another(folder, name, dtype, out, sequences, steps_of):
+    """One replay process for all sequences: each request ends before the next begins, in a
+    pool that holds only the longest, so every request after the first reuses pages."""
+    steps, rows = [], []
+    for key, tokens in sequences.items():
+        own_steps, own_rows = steps_of(key, tokens)
+        for step in own_steps:
+            step["step"] = len(steps)
+            steps.append(step)
+        steps[-1]["end"] = [key]
+        rows += [(key, row) for row in own_rows]
+    pool = pool_for([max(len(t) for t in sequences.values())])
+    logits = run_trace(folder, dtype, steps, out, pool, PAGE_SIZE[name])
+    got = np.concatenate([logits[s["step"]] for s in steps if s["step"] in logits])
+    return got, rows
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompt_alone(tiny, dtype, tmp_path):
     name, folder, sequences, expected = tiny
-    for key, tokens in sequences.items():
-        steps = [{"step": 0, "entries": [{"id": key, "tokens": tokens, "want": list(range(len(tokens)))}], "end": [key]}]
-        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
-        compare(logits[0], expected[key], dtype, f"{name}/{key} whole")
+
+    def whole(key, tokens):
+        return [{"entries": [{"id": key, "tokens": tokens, "want": list(range(len(tokens)))}], "end": []}], range(len(tokens))
+
+    got, rows = run_one_after_another(folder, name, dtype, tmp_path, sequences, whole)
+    compare(got, np.stack([expected[k][r] for k, r in rows]), dtype, f"{name} whole")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_last_32_tokens_one_by_one(tiny, dtype, tmp_path):
     name, folder, sequences, expected = tiny
-    for key, tokens in sequences.items():
+
+    def tail(key, tokens):
         head = max(0, len(tokens) - 32)
         steps, rows = [], []
         if head:
-            steps.append({"step": 0, "entries": [{"id": key, "tokens": tokens[:head], "want": [head - 1]}], "end": []})
+            steps.append({"entries": [{"id": key, "tokens": tokens[:head], "want": [head - 1]}], "end": []})
             rows.append(head - 1)
         for position in range(head, len(tokens)):
-            steps.append({"step": len(steps), "entries": [{"id": key, "tokens": [tokens[position]], "want": [0]}], "end": []})
+            steps.append({"entries": [{"id": key, "tokens": [tokens[position]], "want": [0]}], "end": []})
             rows.append(position)
-        steps[-1]["end"] = [key]
-        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
-        got = np.concatenate([logits[s["step"]] for s in steps])
-        compare(got, expected[key][rows], dtype, f"{name}/{key} decode tail")
+        return steps, rows
+
+    got, rows = run_one_after_another(folder, name, dtype, tmp_path, sequences, tail)
+    compare(got, np.stack([expected[k][r] for k, r in rows]), dtype, f"{name} decode tail")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_portions_of_changing_size(tiny, dtype, tmp_path):
     name, folder, sequences, expected = tiny
     sizes = [7, 2, 5, 3, 2, 16, 2, 9, 4, 2, 31, 2]
-    for key, tokens in sequences.items():
+
+    def portions(key, tokens):
         steps, rows, at, turn = [], [], 0, 0
         while at < len(tokens):
             n = min(sizes[turn % len(sizes)], len(tokens) - at)
-            if len(tokens) - at - n == 1:  # never leave a portion below two tokens by accident
+            if len(tokens) - at - n == 1:  # do not leave a single token for the last portion
                 n += 1
             want = [0, n - 1] if n > 1 else [0]
-            steps.append({"step": len(steps), "entries": [{"id": key, "tokens": tokens[at : at + n], "want": want}], "end": []})
+            steps.append({"entries": [{"id": key, "tokens": tokens[at : at + n], "want": want}], "end": []})
             rows += [at + w for w in want]
             at += n
             turn += 1
-        steps[-1]["end"] = [key]
-        logits = run_trace(folder, dtype, steps, tmp_path / key, pool_for([len(tokens)]), PAGE_SIZE[name])
-        got = np.concatenate([logits[s["step"]] for s in steps])
-        compare(got, expected[key][rows], dtype, f"{name}/{key} portions")
+        return steps, rows
+
+    got, rows = run_one_after_another(folder, name, dtype, tmp_path, sequences, portions)
+    compare(got, np.stack([expected[k][r] for k, r in rows]), dtype, f"{name} portions")
 
 
 def mixed_trace(sequences: dict[str, list[int]], live_limit: int = 4):

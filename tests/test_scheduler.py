@@ -1,0 +1,195 @@
+"""The scheduler's decisions (host code, no GPU): a fake model picks the tokens."""
+
+from __future__ import annotations
+
+import pytest
+
+from llm_inference_b200.csrc.host_module import host
+
+
+def make(h, *, pages=16, page=4, seqs=3, context=64, budget=12, chunk=4, burst=8, vocab=50):
+    cache = h.CacheManager(page, [h.GroupSpec("full", pages, 0)], 0, burst)
+    return cache, h.Scheduler(cache, seqs, context, budget, chunk, burst, vocab, 1)
+
+
+def run_step(s, pick=lambda entry: 9):
+    plan = s.plan()
+    tokens = [pick(e) for e in plan.entries if e.wants_token]
+    return plan, s.commit(plan, tokens)
+
+
+def test_lifecycle_portions_and_first_token():
+    h = host()
+    cache, s = make(h)
+    rid = s.submit(list(range(11)), 3, [], h.SamplingParams())
+    assert s.request(rid).state == "waiting"
+    plan, events = run_step(s)
+    # Nothing decodes, so the portion is the burst size (8); the prompt is not done yet.
+    assert [(e.start, e.count, e.wants_token, e.decode) for e in plan.entries] == [(0, 8, False, False)]
+    assert events == [] and s.request(rid).state == "prefilling"
+    plan, events = run_step(s)
+    assert [(e.start, e.count, e.wants_token) for e in plan.entries] == [(8, 3, True)]
+    assert plan.tokens.tolist() == [8, 9, 10]
+    assert [(e.token, e.finished) for e in events] == [(9, False)] and s.request(rid).state == "running"
+    plan, events = run_step(s, lambda e: 7)
+    assert [(e.start, e.count, e.decode) for e in plan.entries] == [(11, 1, True)] and plan.tokens.tolist() == [9]
+    plan, events = run_step(s, lambda e: 8)
+    assert events[0].finished and events[0].reason == "length"
+    request = s.request(rid)
+    assert request.state == "completed" and request.output == [9, 7, 8]
+    assert cache.stats()["kv_pools"]["full"]["used_pages"] == 0 and not s.has_work()
+    s.forget(rid)
+    with pytest.raises(IndexError):
+        s.request(rid)
+
+
+def test_decode_first_then_prompt_portions_under_the_budget():
+    h = host()
+    cache, s = make(h, budget=7, chunk=4, burst=6)
+    a = s.submit([1] * 6, 5, [], h.SamplingParams())
+    run_step(s)  # a: whole prompt in one burst, first token
+    b = s.submit([2] * 9, 2, [], h.SamplingParams())
+    c = s.submit([3] * 5, 2, [], h.SamplingParams())
+    plan, _ = run_step(s)
+    # One decode token, then b's chunk (4), then what is left of the budget (2) for c.
+    assert [(e.request_id, e.count, e.decode) for e in plan.entries] == [(a, 1, True), (b, 4, False), (c, 2, False)]
+    assert plan.total_tokens == 7
+    plan, _ = run_step(s)
+    assert [(e.request_id, e.start, e.count) for e in plan.entries] == [(a, 7, 1), (b, 4, 4), (c, 2, 2)]
+    plan, events = run_step(s)
+    assert [(e.request_id, e.start, e.count, e.wants_token) for e in plan.entries] == [
+        (a, 8, 1, True), (b, 8, 1, True), (c, 4, 1, True)]
+    assert sorted(e.request_id for e in events) == [a, b, c]
+
+
+def test_stop_token_context_limit_and_forced_tokens():
+    h = host()
+    cache, s = make(h, context=8)
+    a = s.submit([1, 2, 3], 5, [4], h.SamplingParams())
+    _, events = run_step(s, lambda e: 4)
+    assert events[0].reason == "stop" and s.request(a).output == [4]
+    b = s.submit([1, 2, 3, 4, 5], 3, [], h.SamplingParams())
+    run_step(s)
+    _, events = run_step(s)
+    _, events = run_step(s)
+    # length 7 after the third token's step: 7 + 1 >= 8
+    assert events[0].finished and events[0].reason in ("context", "length")
+    c = s.submit([1, 2, 3, 4, 5, 6], 2, [], h.SamplingParams())
+    run_step(s)
+    _, events = run_step(s)
+    assert events[0].reason == "length" or events[0].reason == "context"
+    d = s.submit([1], 3, [], h.SamplingParams())
+    s.force(d, [30, 31])
+    outputs = []
+    while s.has_work():
+        _, events = run_step(s, lambda e: 9)
+        outputs += [e.token for e in events]
+    assert outputs == [30, 31, 9]
+
+
+def test_budget_that_ends_at_the_context_limit():
+    h = host()
+    cache, s = make(h, context=6)
+    with pytest.raises(ValueError, match="exceed the 6-token context"):
+        s.submit([1, 2, 3], 4, [], h.SamplingParams())
+    s.submit([1, 2, 3], 3, [], h.SamplingParams())
+    reasons = []
+    while s.has_work():
+        _, events = run_step(s)
+        reasons += [e.reason for e in events]
+    # The token budget and the context end together; the budget is reported first, as in
+    # the reference's order of checks (python/instinct/mlx_engine.py:517-524).
+    assert reasons == ["", "", "length"]
+
+
+def test_invalid_requests_are_refused_at_submit():
+    h = host()
+    cache, s = make(h, pages=4, context=64)
+    p = h.SamplingParams()
+    for prompt, new, stop, message in [
+        ([], 1, [], "non-empty"),
+        ([50], 1, [], "outside the vocabulary"),
+        ([-1], 1, [], "outside the vocabulary"),
+        ([1], 1, [99], "outside the vocabulary"),
+        ([1], 0, [], "positive integer"),
+        ([1] * 60, 5, [], "exceed the 64-token context"),
+        ([1] * 10, 7, [], "more K/V memory than the cache has"),  # 17 tokens = 5 pages > 4
+    ]:
+        with pytest.raises(ValueError, match=message):
+            s.submit(prompt, new, stop, p)
+    assert s.stats()["submitted"] == 0 and s.stats()["rejected"] == 1
+    for bad in [dict(temperature=-1.0), dict(temperature=11.0), dict(top_p=0.0), dict(top_p=1.5), dict(top_k=-1), dict(min_p=1.0)]:
+        with pytest.raises(ValueError):
+            h.SamplingParams(**bad)
+
+
+def test_when_pages_run_out_requests_wait_in_order():
+    h = host()
+    cache, s = make(h, pages=6, page=4, seqs=4, budget=32, chunk=8, burst=8)
+    p = h.SamplingParams()
+    a = s.submit([1] * 8, 8, [], p)  # 4 pages
+    b = s.submit([2] * 8, 4, [], p)  # 3 pages: does not fit beside a
+    c = s.submit([3] * 2, 2, [], p)  # 1 page: would fit, but may not overtake b
+    plan, _ = run_step(s)
+    assert [e.request_id for e in plan.entries] == [a]
+    assert s.request(b).state == "waiting" and s.request(c).state == "waiting"
+    assert cache.stats()["allocation_failures"] >= 1
+    order = []
+    while s.has_work():
+        plan, events = run_step(s)
+        for e in plan.entries:
+            if e.request_id not in order:
+                order.append(e.request_id)
+        cache.check_invariants()
+    assert order == [a, b, c]  # first come, first served
+    assert all(s.request(r).state == "completed" for r in (a, b, c))
+    assert cache.stats()["kv_pools"]["full"]["used_pages"] == 0
+    assert cache.stats()["kv_pools"]["full"]["reserved_pages"] == 0
+
+
+def test_sequence_limit_and_cancel():
+    h = host()
+    cache, s = make(h, seqs=2, pages=32)
+    p = h.SamplingParams()
+    ids = [s.submit([1] * 5, 4, [], p) for _ in range(3)]
+    plan, _ = run_step(s)
+    assert [e.request_id for e in plan.entries] == ids[:2]
+    s.cancel(ids[0])  # mid-run: its pages return at once
+    assert s.request(ids[0]).state == "cancelled" and s.request(ids[0]).reason == "cancelled"
+    s.cancel(ids[2])  # still waiting
+    with pytest.raises(RuntimeError, match="cannot forget an active request"):
+        s.forget(ids[1])
+    while s.has_work():
+        run_step(s)
+    assert s.request(ids[1]).state == "completed"
+    stats = s.stats()
+    assert (stats["submitted"], stats["completed"], stats["cancelled"]) == (3, 1, 2)
+    assert cache.stats()["kv_pools"]["full"]["used_pages"] == 0
+
+
+def test_cancel_between_plan_and_commit_and_abandon():
+    h = host()
+    cache, s = make(h)
+    p = h.SamplingParams()
+    a = s.submit([1, 2, 3], 4, [], p)
+    b = s.submit([1, 2], 4, [], p)
+    plan = s.plan()
+    s.cancel(a)
+    events = s.commit(plan, [9, 9])
+    assert [e.request_id for e in events] == [b]
+    plan = s.plan()
+    s.abandon(plan)  # the model step threw
+    assert s.request(b).state == "cancelled" and s.request(b).reason == "error"
+    assert cache.stats()["kv_pools"]["full"]["used_pages"] == 0 and not s.has_work()
+
+
+def test_draw_keys_follow_the_seed_and_the_step():
+    h = host()
+    cache, s = make(h)
+    a = s.submit([1], 3, [], h.SamplingParams(temperature=0.8, seed=12345))
+    b = s.submit([1], 3, [], h.SamplingParams(temperature=0.8))
+    assert s.draw_key(a) == (12345 * 1_000_003) % (1 << 63)
+    run_step(s)
+    assert s.draw_key(a) == (12345 * 1_000_003 + 1) % (1 << 63)
+    assert s.draw_key(b) != s.draw_key(a)
+    assert not s.request(a).sampling.greedy and h.SamplingParams(temperature=0.8, top_k=1).greedy
