@@ -1,0 +1,198 @@
+"""Generation through the Python entry point: scheduler, step function, sampling together."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from helpers import PAGE_SIZE, TINY, TOLERANCE, make_model_folder, plain_weights, random_tokens
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request, tmp_path_factory):
+    name = request.param
+    folder = make_model_folder(tmp_path_factory.mktemp(f"engine{name}"), TINY[name], seed=23 + ord(name))
+    config, weights = plain_weights(folder)
+    return name, folder, config, weights
+
+
+def engine_for(name, folder, dtype="float32", **options):
+    from llm_inference_b200 import create_engine
+
+    settings = dict(
+        max_num_sequences=4, kv_cache_bytes=1 << 20, prefill_chunk_size=7, prefill_burst_size=16,
+        page_size=PAGE_SIZE[name], dtype=dtype,
+    )
+    settings.update(options)
+    return create_engine(folder, **settings)
+
+
+def drained(engine) -> bool:
+    pools = engine.stats()["kv_pools"].values()
+    return all(p["used_pages"] == 0 and p["reserved_pages"] == 0 for p in pools)
+
+
+def run_all(engine, prompts, count, **options):
+    ids = [engine.submit(p, count, **options) for p in prompts]
+    while engine.has_work():
+        engine.step()
+    return [engine.request(i).output for i in ids]
+
+
+@pytest.mark.parametrize("length", [1, 3, 7, 8, 9, 16, 17, 33, 60])
+def test_prefill_logits_across_page_and_chunk_edges(tiny, length):
+    name, folder, config, weights = tiny
+    prompt = random_tokens(np.random.default_rng(length), config["vocab_size"], length)
+    with engine_for(name, folder) as engine:
+        got = engine.prefill_logits(prompt)
+        assert drained(engine)
+    want = plain.forward(config, weights, prompt)[-1]
+    assert np.abs(got - want).max() <= TOLERANCE["float32"]
+
+
+def test_greedy_generation_matches_plain(tiny):
+    name, folder, config, weights = tiny
+    prompt = random_tokens(np.random.default_rng(1), config["vocab_size"], 6)
+    count = 90 if name == "A" else 60  # long decoding: many pages, and past the window for B
+    want = plain.greedy(config, weights, prompt, count)
+    with engine_for(name, folder) as engine:
+        assert engine.generate(prompt, count) == want
+        assert drained(engine)
+        assert engine.stats()["generated_tokens"] == count
+
+
+def test_bfloat16_greedy_follows_plain_until_a_near_tie(tiny):
+    name, folder, config, weights = tiny
+    prompt = random_tokens(np.random.default_rng(2), config["vocab_size"], 9)
+    with engine_for(name, folder, dtype="bfloat16") as engine:
+        got = engine.generate(prompt, 24)
+    tokens = list(prompt)
+    for step, token in enumerate(got):
+        logits = plain.forward(config, weights, tokens)[-1]
+        best = int(np.argmax(logits))
+        if token != best:
+            # Allowed only where bfloat16 rounding can flip the order; later tokens then differ.
+            assert logits[best] - logits[token] <= 2 * TOLERANCE["bfloat16"], f"step {step}"
+            break
+        tokens.append(token)
+
+
+def test_batched_requests_match_running_alone(tiny):
+    name, folder, config, weights = tiny
+    vocab = config["vocab_size"]
+    prompts = [[(i * 7 + j) % vocab for i in range(n)] for j, n in enumerate([1, 4, 9, 13, 21, 30])]
+    with engine_for(name, folder, max_num_sequences=3) as engine:
+        alone = [engine.generate(p, 8) for p in prompts]
+        together = run_all(engine, prompts, 8)
+        assert together == alone
+        assert drained(engine)
+    assert alone[2] == plain.greedy(config, weights, prompts[2], 8)
+
+
+def test_seeded_sampling_is_independent_of_the_batch(tiny):
+    from llm_inference_b200 import SamplingParams
+
+    name, folder, config, weights = tiny
+    vocab = config["vocab_size"]
+    rng = np.random.default_rng(3)
+    prompts = [random_tokens(rng, vocab, n) for n in (1, 23, 40, 70)]
+    seeded = SamplingParams(temperature=0.8, seed=1234)
+    with engine_for(name, folder) as engine:
+        alone = engine.generate(prompts[1], 12, sampling=seeded)
+        ids = [
+            engine.submit(prompts[0], 12),
+            engine.submit(prompts[1], 12, sampling=seeded),
+            engine.submit(prompts[2], 12, sampling=SamplingParams(temperature=0.8, seed=77)),
+            engine.submit(prompts[3], 12, sampling=SamplingParams(temperature=1.5, top_k=5)),
+        ]
+        # Staggered arrivals: the later prompts join while the first are decoding.
+        while engine.has_work():
+            engine.step()
+        outputs = [engine.request(i).output for i in ids]
+        assert outputs[1] == alone
+        assert outputs[0] == plain.greedy(config, weights, prompts[0], 12)
+        assert engine.generate(prompts[1], 12, sampling=SamplingParams(temperature=0.8, top_k=1)) == plain.greedy(
+            config, weights, prompts[1], 12
+        )
+        assert drained(engine)
+    # Each seeded draw is the plain sampler's inverse-CDF pick at the engine's own uniform.
+    tokens = list(prompts[1])
+    for step, token in enumerate(alone):
+        logits = plain.forward(config, weights, tokens)[-1]
+        probs = plain.surviving_probabilities(logits, 0.8)
+        cdf = np.cumsum(probs)
+        u = plain.uniform_from_key(plain.draw_key(1234, step))
+        expected = int(np.searchsorted(cdf, u * cdf[-1], side="right"))
+        if token != expected:
+            # Only a draw that lands within rounding of a boundary of the CDF may differ.
+            assert min(abs(u * cdf[-1] - cdf[expected]), abs(u * cdf[-1] - cdf[max(expected - 1, 0)])) < 1e-4
+            break
+        tokens.append(token)
+
+
+def test_window_pool_stays_bounded(tmp_path_factory):
+    folder = make_model_folder(tmp_path_factory.mktemp("window"), TINY["B"], seed=5)
+    with engine_for("B", folder, prefill_chunk_size=8, prefill_burst_size=8) as engine:
+        rid = engine.submit([1] * 40, 150)
+        peak_window, peak_full = 0, 0
+        while engine.has_work():
+            engine.step()
+            pools = engine.stats()["kv_pools"]
+            peak_window = max(peak_window, pools["window24"]["used_pages"])
+            peak_full = max(peak_full, pools["full"]["used_pages"])
+        assert len(engine.request(rid).output) == 150
+        assert peak_window <= 5  # ceil((24 + 8) / 8) + 1
+        assert peak_full == (40 + 150 - 1 + 7) // 8
+        assert drained(engine)
+
+
+def test_cancel_errors_and_close(tiny):
+    name, folder, config, weights = tiny
+    engine = engine_for(name, folder)
+    rid = engine.submit([1] * 30, 4)
+    engine.step()  # part of the prompt is in the cache
+    assert engine.request(rid).state.value == "prefilling"
+    engine.cancel(rid)
+    assert engine.request(rid).state.value == "cancelled" and drained(engine)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        engine.submit([config["vocab_size"]], 1)
+    with pytest.raises(ValueError, match="exceed"):
+        engine.submit([1] * 100, config["max_position_embeddings"])
+    with pytest.raises(ValueError, match="positive integer"):
+        engine.submit([1], 0)
+    with pytest.raises(ValueError, match="non-empty"):
+        engine.submit([], 3)
+    rid = engine.submit([3, 4], 5, eos_token_ids=[9])
+    engine.force(rid, [8, 9])
+    events = []
+    while engine.has_work():
+        events += engine.step()
+    assert [(e.token, e.finished, e.reason) for e in events] == [(8, False, ""), (9, True, "stop")]
+    stats = engine.stats()
+    for key in ("submitted", "completed", "cancelled", "prompt_tokens", "generated_tokens", "steps", "running",
+                "waiting", "kv_pools", "kv_device_bytes", "allocation_failures", "live_tokens", "weight_bytes"):
+        assert key in stats
+    engine.close()
+    with pytest.raises(RuntimeError, match="closed"):
+        engine.step()
+
+
+def test_requests_wait_when_pages_run_out(tiny):
+    name, folder, config, weights = tiny
+    page = PAGE_SIZE[name]
+    # Room for about two of these requests at a time.
+    with engine_for(name, folder, num_pages=(2 * 48) // page + 1, max_num_sequences=4) as engine:
+        prompts = [[(3 * i + j) % 200 + 1 for i in range(30)] for j in range(5)]
+        ids = [engine.submit(p, 12) for p in prompts]
+        most_running = 0
+        while engine.has_work():
+            engine.step()
+            most_running = max(most_running, engine.stats()["running"])
+        assert most_running <= 2 and engine.stats()["allocation_failures"] > 0
+        assert [engine.request(i).output for i in ids] == [plain.greedy(config, weights, p, 12) for p in prompts]
+        assert drained(engine)
+        with pytest.raises(ValueError, match="more K/V memory than the cache has"):
+            engine.submit([1] * 100, 20)

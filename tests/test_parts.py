@@ -1,0 +1,245 @@
+"""Each part alone against the plain implementation, and a toy mixer with state of its own
+that is registered, built and stepped without touching the framework."""
+
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOLERANCE
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+
+def context_for(cache_specs, dtype, runs, starts=None, page_size=8, wanted=()):
+    """A real step context (and cache) for requests that feed ``runs[i]`` tokens each."""
+    from llm_inference_b200.cache import PagedCache
+    from llm_inference_b200.engine.runner import ModelRunner, StepEntry
+
+    device = torch.device("cuda:0")
+    cache = PagedCache(cache_specs, dtype=dtype, device=device, page_size=page_size, max_num_sequences=8,
+                       max_model_length=256, step_tokens=64, num_pages=64)
+    stub = SimpleNamespace(device=device, dtype=dtype)
+    runner = ModelRunner(stub, cache, max_batch_tokens=512)
+    entries = []
+    starts = starts or [0] * len(runs)
+    for i, (run, start) in enumerate(zip(runs, starts)):
+        cache.open(i + 1)
+        cache.manager.ensure(i + 1, start)
+        cache.manager.advance(i + 1, start)
+        entries.append(StepEntry(i + 1, [0] * run))
+    ctx = runner._build_context(entries, starts, list(wanted))
+    return runner, cache, ctx
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_feed_forward_embedding_and_head_parts(dtype):
+    from llm_inference_b200.parts import PartSpec, build_part
+    from llm_inference_b200.weights import random_weights
+
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    hidden, inter, vocab, tokens = 72, 200, 130, 11
+    runner, cache, ctx = context_for({}, dtype, [tokens], wanted=[0, 10, 3])
+    norm = build_part("norm", PartSpec("rmsnorm", dict(name="n", hidden_size=hidden, eps=1e-5)))
+    ffn = build_part("feed_forward", PartSpec("swiglu", dict(prefix="mlp.", hidden_size=hidden, intermediate_size=inter)))
+    embedding = build_part("embedding", PartSpec("token_embedding", dict(name="emb", vocab_size=vocab, hidden_size=hidden)))
+    head = build_part("head", PartSpec("linear_head", dict(name="head", vocab_size=vocab, hidden_size=hidden, tied_to="emb")))
+    specs = norm.tensor_specs() + ffn.tensor_specs() + embedding.tensor_specs()
+    weights = random_weights(specs, seed=9, std=0.3)
+    for part in (norm, ffn, embedding, head):
+        part.load(weights, dtype, ctx.device)
+    as64 = {k: v.double().numpy() for k, v in weights.items()}
+    ids = torch.randint(0, vocab, (tokens,), dtype=torch.int32)
+    ctx.token_ids.copy_(ids.cuda())
+    x = embedding.forward(ctx)
+    assert x.dtype == torch.float32 and torch.equal(x.cpu(), weights["emb.weight"].float()[ids.long()])
+    delta = (torch.randn(tokens, hidden) * 0.5).to(dtype).cuda()
+    want_x = x.double().cpu().numpy() + delta.double().cpu().numpy()
+    h = norm.forward(ctx, x, delta)
+    np.testing.assert_allclose(h.double().cpu().numpy(), plain.rms_norm(want_x, as64["n.weight"], 1e-5), atol=TOLERANCE[name], rtol=1e-2)
+    out = ffn.forward(ctx, h)
+    want = plain.swiglu(h.double().cpu().numpy(), as64["mlp.gate_proj.weight"], as64["mlp.up_proj.weight"], as64["mlp.down_proj.weight"])
+    np.testing.assert_allclose(out.double().cpu().numpy(), want, atol=20 * TOLERANCE[name], rtol=2e-2)
+    rows = norm.forward(ctx, x, None, rows=ctx.logit_rows, out_name="rows")
+    logits = head.forward(ctx, rows)
+    assert logits.dtype == torch.float32 and logits.shape == (3, vocab)
+    want = plain.linear(rows.double().cpu().numpy(), as64["emb.weight"])
+    np.testing.assert_allclose(logits.double().cpu().numpy(), want, atol=10 * TOLERANCE[name], rtol=1e-2)
+    assert head.weight is embedding.table
+
+
+def test_rotary_table_matches_plain():
+    from llm_inference_b200.parts import PartSpec, build_part
+
+    for dims, theta in ((16, 1e4), (32, 1e6), (128, 1e6)):
+        part = build_part("position", PartSpec("rotary", dict(head_dim=dims, theta=theta)))
+        assert np.array_equal(part.table(), plain.rope_inverse_frequencies(dims, theta))
+    partial = build_part("position", PartSpec("rotary", dict(head_dim=64, theta=1e4, rotary_dims=16)))
+    assert np.array_equal(partial.table(), plain.rope_inverse_frequencies(16, 1e4))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 5])
+def test_attention_mixer_alone_in_portions(dtype, window):
+    """One attention part, fed a sequence in three portions beside another request."""
+    from llm_inference_b200.engine.runner import StepEntry
+    from llm_inference_b200.parts import PartSpec, build_part
+    from llm_inference_b200.weights import random_weights
+
+    name = "float32" if dtype == torch.float32 else "bfloat16"
+    hidden, q_heads, kv_heads, dim, theta = 40, 6, 2, 16, 5e4
+    mixer = build_part("mixer", PartSpec("gqa_attention", dict(
+        prefix="layers.0.self_attn.", hidden_size=hidden, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim,
+        window=window, position=PartSpec("rotary", dict(head_dim=dim, theta=theta)))))
+    weights = random_weights(mixer.tensor_specs(), seed=4, std=0.2)
+    as64 = {("model." + k): v.double().numpy() for k, v in weights.items()}
+    config = dict(num_attention_heads=q_heads, num_key_value_heads=kv_heads, hidden_size=hidden, head_dim=dim,
+                  rope_theta=theta, use_sliding_window=bool(window), sliding_window=window, max_window_layers=0)
+    total = 19
+    h_all = (torch.randn(total, hidden) * 0.7).to(dtype)
+    other = (torch.randn(6, hidden) * 0.7).to(dtype)
+    want = plain.attention_block(config, as64, 0, h_all.double().numpy(), np.arange(total))
+    runner, cache, _ = context_for({0: mixer.cache_spec()}, dtype, [1])
+    mixer.load(weights, dtype, torch.device("cuda:0"))
+    cache.open(10), cache.open(11)
+    got, at = [], 0
+    for portion in (7, 2, 10):
+        entries = [StepEntry(11, [0] * min(2, 6 - 2 * len(got))), StepEntry(10, [0] * portion)]
+        starts = [cache.manager.length(e.request_id) for e in entries]
+        for e, s in zip(entries, starts):
+            cache.manager.ensure(e.request_id, s + len(e.tokens))
+        ctx = runner._build_context(entries, starts, [])
+        h = torch.cat([other[starts[0] : starts[0] + len(entries[0].tokens)], h_all[at : at + portion]]).cuda()
+        out = mixer.forward(ctx, cache.view(0, True, runner._tables), h)
+        got.append(out[len(entries[0].tokens) :].double().cpu().numpy())
+        for e, s in zip(entries, starts):
+            cache.manager.advance(e.request_id, s + len(e.tokens))
+        at += portion
+    runner.check()
+    np.testing.assert_allclose(np.concatenate(got), want, atol=10 * TOLERANCE[name], rtol=2e-2)
+
+
+# --- a toy architecture whose mixer keeps state of its own -------------------------------------
+
+
+def register_toy():
+    from llm_inference_b200.config import ModelConfig, register_architecture
+    from llm_inference_b200.parts import ModelRecipe, Part, PartSpec, StateSpec, register_part
+    from llm_inference_b200.weights import TensorSpec
+
+    class RunningMeanMixer(Part):
+        """out[t] = W * mean(h[0..t]) of the request: needs a running sum and a count per request."""
+
+        graph_safe = False
+
+        def __init__(self, *, prefix: str, hidden_size: int) -> None:
+            self.prefix, self.hidden_size = prefix, hidden_size
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "mix.weight", (self.hidden_size, self.hidden_size))]
+
+        def load(self, tensors, dtype, device):
+            self.weight = tensors[self.prefix + "mix.weight"].to(device=device, dtype=dtype)
+
+        def cache_spec(self):
+            return StateSpec(((self.hidden_size,), (1,)), (torch.float32, torch.float32))
+
+        def forward(self, ctx, cache, h):
+            sums, counts = cache.state
+            out = torch.empty_like(h)
+            for s in range(ctx.num_seqs):
+                slot = int(ctx.host.seq_slot[s])
+                a, n = int(ctx.host.seq_q_start[s]), int(ctx.host.seq_q_len[s])
+                running = sums[slot] + torch.cumsum(h[a : a + n].float(), 0)
+                seen = counts[slot] + torch.arange(1, n + 1, device=h.device, dtype=torch.float32)[:, None]
+                out[a : a + n] = ((running / seen).to(h.dtype) @ self.weight.t())
+                sums[slot] = running[-1]
+                counts[slot] = seen[-1]
+            return out
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        intermediate_size: int = 0
+        rms_norm_eps: float = 1e-6
+
+        @classmethod
+        def from_json_dict(cls, raw):
+            return cls("ToyStateForCausalLM", raw["vocab_size"], raw["hidden_size"], raw["num_hidden_layers"],
+                       raw["max_position_embeddings"], (), raw["intermediate_size"], raw["rms_norm_eps"])
+
+        def to_json_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                        num_hidden_layers=self.num_hidden_layers, max_position_embeddings=self.max_position_embeddings,
+                        intermediate_size=self.intermediate_size, rms_norm_eps=self.rms_norm_eps)
+
+    def recipe(config):
+        def norm(name):
+            return PartSpec("rmsnorm", dict(name=name, hidden_size=config.hidden_size, eps=config.rms_norm_eps))
+
+        layers = [
+            PartSpec("pre_norm_residual", dict(
+                mixer=PartSpec("running_mean", dict(prefix=f"layers.{i}.", hidden_size=config.hidden_size)),
+                feed_forward=PartSpec("swiglu", dict(prefix=f"layers.{i}.mlp.", hidden_size=config.hidden_size,
+                                                     intermediate_size=config.intermediate_size)),
+                mixer_norm=norm(f"layers.{i}.norm1"), feed_forward_norm=norm(f"layers.{i}.norm2")))
+            for i in range(config.num_hidden_layers)
+        ]
+        return ModelRecipe(
+            config=config,
+            embedding=PartSpec("token_embedding", dict(name="embed", vocab_size=config.vocab_size, hidden_size=config.hidden_size)),
+            layers=layers, final_norm=norm("norm"),
+            head=PartSpec("linear_head", dict(name="head", vocab_size=config.vocab_size, hidden_size=config.hidden_size)))
+
+    register_part("mixer", "running_mean", RunningMeanMixer, replace=True)
+    register_architecture("ToyStateForCausalLM", ToyConfig.from_json_dict, recipe, replace=True)
+    return ToyConfig
+
+
+def toy_plain(config, weights, tokens):
+    x = weights["embed.weight"][tokens]
+    for i in range(config["num_hidden_layers"]):
+        p = f"layers.{i}."
+        h = plain.rms_norm(x, weights[p + "norm1.weight"], config["rms_norm_eps"])
+        means = np.cumsum(h, axis=0) / np.arange(1, len(tokens) + 1)[:, None]
+        x = x + means @ weights[p + "mix.weight"].T
+        h = plain.rms_norm(x, weights[p + "norm2.weight"], config["rms_norm_eps"])
+        x = x + plain.swiglu(h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, weights["norm.weight"], config["rms_norm_eps"]), weights["head.weight"])
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    from helpers import plain_weights, run_trace
+    from llm_inference_b200 import create_engine
+    from llm_inference_b200.weights import write_model_folder
+
+    ToyConfig = register_toy()
+    config = ToyConfig("ToyStateForCausalLM", 97, 48, 2, 64, (), 80, 1e-6)
+    folder = write_model_folder(tmp_path / "toy", config, seed=2, std=0.2)
+    raw, weights = plain_weights(folder)
+    assert json.loads((folder / "config.json").read_text())["architectures"] == ["ToyStateForCausalLM"]
+    rng = np.random.default_rng(0)
+    a = [int(t) for t in rng.integers(0, 97, 21)]
+    b = [int(t) for t in rng.integers(0, 97, 9)]
+    with create_engine(folder, dtype="float32", max_num_sequences=3, kv_cache_bytes=1 << 20, page_size=8,
+                       prefill_chunk_size=4, prefill_burst_size=6) as engine:
+        assert engine.cache.state_slots == 3 and not engine.cache.groups
+        # Whole, then in portions beside another request: the state carries across steps,
+        # and a slot that is handed out again starts from zero.
+        whole = engine.prefill_logits(a)
+        np.testing.assert_allclose(whole, toy_plain(raw, weights, a)[-1], atol=1e-4)
+        ids = [engine.submit(a, 3), engine.submit(b, 3)]
+        while engine.has_work():
+            engine.step()
+        for rid, prompt in zip(ids, (a, b)):
+            tokens, out = list(prompt), []
+            for _ in range(3):
+                out.append(int(np.argmax(toy_plain(raw, weights, tokens)[-1])))
+                tokens.append(out[-1])
+            assert engine.request(rid).output == out
+        assert engine.stats()["free_state_slots"] == 3
