@@ -49,24 +49,29 @@ class CacheView:
 class Workspace:
     """Named scratch buffers that grow to the largest size asked for and are then reused."""
 
-    def __init__(self, device: torch.device) -> None:
+    def __init__(self, device: torch.device, min_rows: int = 0) -> None:
         self.device = device
         self._flat: dict[str, torch.Tensor] = {}
-        self.frozen = False  # set while a CUDA graph that uses these buffers exists
+        # Buffers whose first dimension counts tokens are sized for at least this many rows,
+        # so that a later, larger step does not move them.
+        self.min_rows = min_rows
+        # Bumped whenever a buffer is (re)allocated: addresses captured in a CUDA graph before
+        # that are stale afterwards.
+        self.generation = 0
 
-    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype, *, per_token: bool = True) -> torch.Tensor:
         count = 1
         for s in shape:
             count *= int(s)
         key = f"{name}:{dtype}"
         flat = self._flat.get(key)
         if flat is None or flat.numel() < count:
-            if self.frozen and flat is not None:
-                raise RuntimeError(
-                    f"workspace buffer '{name}' would have to grow while a CUDA graph holds it"
-                )
-            flat = torch.empty(max(count, 1), dtype=dtype, device=self.device)
+            capacity = count
+            if per_token and len(shape) >= 1 and shape[0] < self.min_rows:
+                capacity = count // max(int(shape[0]), 1) * self.min_rows if shape[0] else self.min_rows
+            flat = torch.empty(max(capacity, count, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
+            self.generation += 1
         return flat[:count].view(shape)
 
     def bytes(self) -> int:
@@ -98,8 +103,12 @@ class StepContext:
     max_q_len: int = 0
     options: dict[str, Any] = field(default_factory=dict)
 
-    def buffer(self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None) -> torch.Tensor:
-        return self.workspace.get(name, shape, dtype or self.dtype)
+    def buffer(
+        self, name: str, shape: tuple[int, ...], dtype: torch.dtype | None = None, *, per_token: bool = True
+    ) -> torch.Tensor:
+        """Scratch for this step. ``per_token=False`` marks buffers whose row count is not
+        the step's token count (logits of the wanted rows), which are sized as asked."""
+        return self.workspace.get(name, shape, dtype or self.dtype, per_token=per_token)
 
     @property
     def stream(self):

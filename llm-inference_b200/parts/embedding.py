@@ -59,7 +59,7 @@ class OutputHead(Part):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        logits = ctx.buffer("logits", (h.shape[0], self.vocab_size), torch.float32)
+        logits = ctx.buffer("logits", (h.shape[0], self.vocab_size), torch.float32, per_token=False)
         return ops.linear(ctx, h, self.weight, logits)
 
 

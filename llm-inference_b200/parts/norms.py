@@ -37,7 +37,7 @@ class RMSNorm(Part):
         out_name: str = "normed",
     ) -> torch.Tensor:
         count = x.shape[0] if rows is None else rows.shape[0]
-        out = ctx.buffer(out_name, (count, self.hidden_size))
+        out = ctx.buffer(out_name, (count, self.hidden_size), per_token=rows is None)
         return ops.rmsnorm(ctx, x, delta, self.weight, self.eps, out, rows)
 
 

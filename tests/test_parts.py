@@ -71,6 +71,7 @@ def test_norm_feed_forward_embedding_and_head_parts(dtype):
     assert logits.dtype == torch.float32 and logits.shape == (3, vocab)
     want = plain.linear(rows.double().cpu().numpy(), as64["emb.weight"])
     np.testing.assert_allclose(logits.double().cpu().numpy(), want, atol=10 * TOLERANCE[name], rtol=1e-2)
+    head.share(embedding)  # what Model.load does for a tied head
     assert head.weight is embedding.table
 
 
