@@ -1,0 +1,357 @@
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A *step* is one decode step. The default run uses the layer sizes of the Qwen2.5-1.5B shape
+with seeded random bfloat16 weights, eight requests that each hold a 2,048-token prompt and
+decode inside a 4,096-token context; it prints one JSON line. ``value`` is decoded tokens per
+second timed on the device with CUDA events over K steps of the engine's own step function
+(metadata built on the host, copied, CUDA-graph replay); ``e2e`` is the same through the
+public entry point with the sampled tokens read back to the host every step. Also on the
+line: a 2,048-token prefill, the decode step's achieved bytes per second against the HBM
+peak, and decoding at batch 1 and 64. Peaks come from MEASURED_PEAKS.json beside this file
+when present, else the fallback figures below.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+# Layer sizes of the Qwen2.5-1.5B shape (python/instinct/backends/dense.py is the model).
+MODEL = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "model_type": "qwen2",
+    "num_hidden_layers": 28,
+    "hidden_size": 1536,
+    "num_attention_heads": 12,
+    "num_key_value_heads": 2,
+    "head_dim": 128,
+    "intermediate_size": 8960,
+    "vocab_size": 151936,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "tie_word_embeddings": True,
+    "use_sliding_window": False,
+    "sliding_window": 32768,
+    "max_window_layers": 28,
+    "max_position_embeddings": 32768,
+    "eos_token_id": 151643,
+}
+FULL_LAYERS = MODEL["num_hidden_layers"]
+PROMPT = 2048
+CONTEXT = 4096
+PAGE = 64
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            out = {"source": "measured"}
+            out["hbm_gbs"] = float(raw.get("hbm_gbs") or raw.get("hbm_gb_s") or FALLBACK_PEAKS["hbm_gbs"])
+            out["bf16_tflops"] = float(raw.get("bf16_tflops") or FALLBACK_PEAKS["bf16_tflops"])
+            if raw.get("bf16_tflops_sustained"):
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            return out
+        except (ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self) -> None:
+        self.lines: list[str] = []
+        self.proc = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def mark(self) -> int:
+        return len(self.lines)
+
+    def stop(self) -> None:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, begin: int = 0, end: int | None = None) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        for line in self.lines[begin:end]:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                maxima.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(self.NAMES, parts[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {
+            "sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima), "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def reference_arm() -> int:
+    reason = (
+        "the reference's tested engine needs MLX (Apple/Metal; not installable offline here) and its "
+        "CUDA engine does not compile with CUDA 12.9 (nvToolsExt.h is gone) and has never run on a GPU"
+    )
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    return 0
+
+
+def linear_flops_per_token(config, layers: int) -> float:
+    h, i, d = config.hidden_size, config.intermediate_size, config.head_dim
+    qkv = (config.num_attention_heads + 2 * config.num_key_value_heads) * d * h
+    o = config.num_attention_heads * d * h
+    return 2.0 * layers * (qkv + o + 3 * i * h)
+
+
+def attention_flops(config, layers: int, tokens: int) -> float:
+    return layers * config.num_attention_heads * 4.0 * config.head_dim * tokens * (tokens + 1) / 2.0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
+    parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    parser.add_argument("--no-graphs", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from llm_inference_b200 import models  # noqa: F401
+    from llm_inference_b200.config import parse_config
+    from llm_inference_b200.engine.engine import Engine
+    from llm_inference_b200.engine.loading import random_model
+    from llm_inference_b200.engine.runner import StepEntry
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device is visible", file=sys.stderr)
+        return 1
+    torch.cuda.set_device(0)
+    peak = peaks()
+    raw = dict(MODEL, num_hidden_layers=args.layers, max_window_layers=args.layers)
+    _, config = parse_config(raw)
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    max_batch = max(64, args.batch)
+    steps, warmup = args.steps, args.warmup
+    new_tokens = 256
+    if steps + warmup + 1 > new_tokens:
+        new_tokens = steps + warmup + 1
+    budget_tokens = max_batch * (PROMPT + new_tokens + PAGE)
+    kv_bytes_per_token = 2 * args.layers * config.num_key_value_heads * config.head_dim * 2
+    engine = Engine(
+        model=model, max_num_sequences=max_batch, max_model_length=CONTEXT, kv_cache_bytes=budget_tokens * kv_bytes_per_token,
+        page_size=PAGE, prefill_chunk_size=PROMPT, prefill_burst_size=PROMPT, max_batch_tokens=PROMPT + max_batch,
+        cuda_graphs=not args.no_graphs,
+    )
+    runner, cache = engine.runner, engine.cache
+    rng = np.random.default_rng(0)
+    vocab = config.vocab_size
+    weight_bytes = model.weight_bytes()
+    sampler = ClockSampler()
+    sampler.start()
+
+    def timed(fn, repeat: int) -> float:
+        """Median milliseconds of ``fn`` over ``repeat`` runs, on the device."""
+        times = []
+        for _ in range(repeat):
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            fn()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(end))
+        return statistics.median(times)
+
+    # --- prefill of one 2,048-token prompt -------------------------------------------------------
+    prompt = [int(t) for t in rng.integers(0, vocab, PROMPT)]
+    scratch_id = [10_000]
+
+    def prefill_once() -> None:
+        scratch_id[0] += 1
+        cache.open(scratch_id[0])
+        runner.step([StepEntry(scratch_id[0], prompt, (PROMPT - 1,))])
+        cache.manager.release(scratch_id[0])
+
+    for _ in range(3):
+        prefill_once()
+    prefill_ms = timed(prefill_once, 5)
+    prefill_flops = PROMPT * linear_flops_per_token(config, args.layers) + attention_flops(config, args.layers, PROMPT)
+    prefill_flops += 2.0 * vocab * config.hidden_size
+    prefill = {
+        "value": PROMPT / (prefill_ms / 1e3), "tokens": PROMPT, "ms": prefill_ms,
+        "frac": prefill_flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+    }
+
+    # --- decode, timed on the device -------------------------------------------------------------
+    def decode_point(batch: int, k: int, w: int) -> dict:
+        ids = list(range(20_000 + 1000 * batch, 20_000 + 1000 * batch + batch))
+        for rid in ids:
+            cache.open(rid)
+            runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, vocab, PROMPT)])])
+        feed = rng.integers(0, vocab, size=(w + k, batch))
+
+        def one(step: int) -> None:
+            runner.step([StepEntry(rid, (int(feed[step, j]),), (0,)) for j, rid in enumerate(ids)])
+
+        for step in range(w):
+            one(step)
+        torch.cuda.synchronize()
+        calls_before = runner.lib.calls
+        replays_before = runner.graph_replays
+        mark = sampler.mark()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for step in range(w, w + k):
+            one(step)
+        end.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(end) / k
+        replays = runner.graph_replays - replays_before
+        launches = (runner.lib.calls - calls_before) + replays * runner.launches_per_graph.get(runner._bucket(batch), 0)
+        mean_context = PROMPT + w + k / 2.0
+        step_bytes = weight_bytes + batch * mean_context * kv_bytes_per_token
+        runner.check()
+        for rid in ids:
+            cache.manager.release(rid)
+        return {
+            "tokens_per_s": batch * 1e3 / ms, "ms_per_step": ms, "bytes": step_bytes, "launches": launches,
+            "clocks": sampler.summary(mark, sampler.mark()),
+        }
+
+    main_point = decode_point(args.batch, steps, warmup)
+    points = {}
+    if not args.no_points:
+        for batch in (1, 64):
+            points[f"decode_b{batch}"] = decode_point(batch, max(16, steps // 2), warmup)["tokens_per_s"]
+
+    # --- the same through the public entry point: host tokens in and out ------------------------
+    prompts = [[int(t) for t in rng.integers(0, vocab, PROMPT)] for _ in range(args.batch)]
+    request_ids = [engine.submit(p, new_tokens) for p in prompts]
+    while any(engine.request(r).state.value in ("waiting", "prefilling") for r in request_ids):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    emitted = 0
+    for _ in range(steps):
+        emitted += len(engine.step())
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - begin
+    for r in request_ids:
+        engine.cancel(r)
+    layout_words = 3 * args.batch + 4 * args.batch + args.batch + args.batch * cache.max_pages_per_request
+    e2e = {
+        "value": emitted / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": 4 * layout_words,
+        "d2h_bytes_per_step": 4 * (args.batch + 1),
+    }
+    sampler.stop()
+
+    achieved = main_point["bytes"] / (main_point["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s (batch 8, 2,048-token prompts, Qwen2.5-1.5B shape)",
+        "value": main_point["tokens_per_s"],
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": main_point["ms_per_step"],
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0,0.02), token ids uniform in the vocabulary",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-1.5B shape",
+            "layers": args.layers,
+            "layers_full": FULL_LAYERS,
+            "hidden": config.hidden_size,
+            "q_heads": config.num_attention_heads,
+            "kv_heads": config.num_key_value_heads,
+            "head_dim": config.head_dim,
+            "intermediate": config.intermediate_size,
+            "vocab": config.vocab_size,
+            "tied_head": config.tie_word_embeddings,
+            "global_batch": args.batch,
+            "seq_len": CONTEXT,
+            "prompt_len": PROMPT,
+            "page_size": PAGE,
+            "parallelism": "single GPU",
+            "cuda_graphs": not args.no_graphs,
+            "l2": "inputs larger than L2: each step reads all weights (GBs)",
+            "peaks": peak["source"],
+        },
+        "e2e": e2e,
+        "gpu_launches": main_point["launches"],
+        "prefill": prefill,
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peak["hbm_gbs"],
+        },
+        "points": points,
+        "clocks": main_point["clocks"],
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -67,6 +67,7 @@ class KernelLibrary:
         self.lib.b200_last_error.restype = ctypes.c_char_p
         self.lib.b200_abi_version.restype = c_int
         self._functions = {}
+        self.calls = 0  # kernel launches issued through this library
         for name, argtypes in _SIGNATURES.items():
             self.bind(name, argtypes)
 
@@ -84,6 +85,7 @@ class KernelLibrary:
 
     def call(self, name: str, *args) -> None:
         status = self._functions[name](*args)
+        self.calls += 1
         if status != 0:
             raise KernelError(self.lib.b200_last_error().decode(errors="replace"))
 

@@ -137,7 +137,10 @@ class Engine:
             num_pages=num_pages,
         )
         self.runner = ModelRunner(
-            model, self.cache, max_batch_tokens=self.max_batch_tokens, options={"cuda_graphs": cuda_graphs}
+            model,
+            self.cache,
+            max_batch_tokens=self.max_batch_tokens,
+            options={"cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens},
         )
         self.sampler = Sampler(self.device, max_num_sequences)
         self._host = host()

@@ -102,13 +102,23 @@ class ModelRunner:
         self.device, self.dtype = model.device, model.dtype
         self.lib = kernels()
         self.max_batch_tokens = max_batch_tokens
-        self.workspace = Workspace(self.device)
-        self.staging = _Staging(self.device)
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.options = dict(options or {})
+        self.workspace = Workspace(self.device, min_rows=min(max_batch_tokens, int(self.options.get("workspace_rows", 0))))
+        self.staging = _Staging(self.device)
+        # The metadata buffers never move after this: CUDA graphs hold their addresses.
+        groups = len(cache.groups)
+        seqs = max_batch_tokens  # a step never holds more requests than tokens
+        self.staging.reserve(_Layout(max_batch_tokens, seqs, max_batch_tokens, cache.max_pages_per_request, groups).total)
+        self.staging.frozen = True
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps = 0
         self.tokens_run = 0
-        self.kernel_launches = 0
+        # Decode-only steps replay a CUDA graph per batch-size bucket (see _decode_graph).
+        self.use_graphs = bool(self.options.get("cuda_graphs", True)) and bool(getattr(model, "graph_safe", False))
+        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graph_generation = -1
+        self.graph_replays = 0
+        self.launches_per_graph: dict[int, int] = {}
 
     # ------------------------------------------------------------------------------------------
 
@@ -150,9 +160,12 @@ class ModelRunner:
 
         ordered = [entries[i] for i in order]
         ordered_starts = [starts[i] for i in order]
-        ctx = self._build_context(ordered, ordered_starts, wanted_rows)
-        tables = self._tables
-        logits = self.model.forward(ctx, lambda call: self._view(call, tables))
+        if self.use_graphs and total == len(entries) and len(entries) <= self.cache.max_num_sequences:
+            logits = self._decode_graph(ordered, ordered_starts, wanted_rows)
+        else:
+            ctx = self._build_context(ordered, ordered_starts, wanted_rows)
+            tables = self._tables
+            logits = self.model.forward(ctx, lambda call: self._view(call, tables))
         for e, start in zip(entries, starts):
             manager.advance(e.request_id, start + len(e.tokens))
         self.steps += 1
@@ -170,9 +183,63 @@ class ModelRunner:
     def _view(self, call: LayerCall, tables):
         return self.cache.view(call.cache_id, call.writes, tables)
 
-    def _build_context(self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int]) -> StepContext:
+    # -- decode steps as CUDA graphs ---------------------------------------------------------------
+    #
+    # A step in which every request feeds one token launches the same kernels with the same
+    # arguments every time, once its batch is padded to a fixed size: all that changes lives
+    # in the metadata buffer (tokens, positions, lengths, block tables), which the kernels
+    # read on the device. So such a step is captured once per batch-size bucket and
+    # replayed. Padding rows are requests of length one whose table points at the arena's
+    # spare page. The first step of a bucket runs eagerly (that run's results are used) and
+    # is then captured for the following ones.
+
+    def _bucket(self, count: int) -> int:
+        bucket = 1
+        while bucket < count:
+            bucket *= 2
+        return min(bucket, max(self.cache.max_num_sequences, count))
+
+    def _decode_graph(self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int]) -> torch.Tensor:
+        count = len(entries)
+        bucket = self._bucket(count)
+        if self._graph_generation != self.workspace.generation:
+            self._graphs.clear()  # a scratch buffer moved: captured addresses are stale
+        ctx = self._build_context(entries, starts, list(range(bucket)), pad_to=bucket)
+        tables = self._tables
+        cached = self._graphs.get(bucket)
+        if cached is None:
+            calls_before = self.lib.calls
+            logits = self.model.forward(ctx, lambda call: self._view(call, tables))
+            self.launches_per_graph[bucket] = self.lib.calls - calls_before
+            if self._graph_generation != self.workspace.generation:
+                # The eager run allocated scratch; capture on the next step, when nothing moves.
+                self._graph_generation = self.workspace.generation
+                self._graphs.clear()
+            else:
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.current_stream(self.device).synchronize()
+                with torch.cuda.graph(graph):
+                    captured = self.model.forward(ctx, lambda call: self._view(call, tables))
+                self._graphs[bucket] = (graph, captured, self.workspace.generation)
+        else:
+            graph, logits, _ = cached
+            graph.replay()
+            self.graph_replays += 1
+        if wanted_rows == list(range(count)):
+            return logits[:count]
+        return logits[torch.tensor(wanted_rows, dtype=torch.long, device=self.device)]
+
+    def _build_context(
+        self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int], pad_to: int | None = None
+    ) -> StepContext:
+        """Lay the step's metadata out in the pinned buffer, copy it to the device and wrap it.
+        With ``pad_to`` (single-token steps only) the batch is filled up to that many requests
+        with rows that write to the arenas' spare page."""
+        real = len(entries)
         t = sum(len(e.tokens) for e in entries)
         s = len(entries)
+        if pad_to is not None:
+            t = s = pad_to
         w = len(wanted_rows)
         groups = len(self.cache.groups)
         layout = _Layout(t, s, w, self.cache.max_pages_per_request, groups)
@@ -208,6 +275,17 @@ class ModelRunner:
             host_view(layout.tables[g], s * layout.max_pages).reshape(s, layout.max_pages) for g in range(groups)
         ]
         self.cache.fill_tables(ids, table_views)
+        if s > real:
+            token_ids[real:] = 0
+            positions[real:] = 0
+            token_seq[real:] = np.arange(real, s, dtype=np.int32)
+            q_start[real:] = np.arange(real, s, dtype=np.int32)
+            q_len[real:] = 1
+            kv_len[real:] = 1
+            slot[real:] = -1
+            for group in self.cache.groups:
+                table_views[group.index][real:] = self.cache.null_page(group)
+            decode = s
         dev = self.staging.dev
         dev[: layout.total].copy_(self.staging.host[: layout.total], non_blocking=True)
         self.staging.copied.record()
@@ -239,7 +317,9 @@ class ModelRunner:
             err=self.err,
             workspace=self.workspace,
             num_decode_seqs=decode,
-            max_kv_len=int(kv_len.max()),
+            # A captured step must launch for the longest request the engine allows.
+            max_kv_len=int(kv_len.max()) if pad_to is None else self.cache.max_pages_per_request * self.cache.page_size,
             max_q_len=int(q_len.max()),
+            captured=pad_to is not None,
             options=self.options,
         )

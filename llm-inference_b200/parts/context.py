@@ -101,6 +101,7 @@ class StepContext:
     num_decode_seqs: int = 0  # the first this-many requests of the batch feed a single token
     max_kv_len: int = 0
     max_q_len: int = 0
+    captured: bool = False  # the step is (or will be) replayed from a CUDA graph
     options: dict[str, Any] = field(default_factory=dict)
 
     def buffer(
