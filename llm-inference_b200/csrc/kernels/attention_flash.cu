@@ -1,0 +1,507 @@
+// Paged flash attention on tensor cores for bfloat16: prefill portions and decoded tokens.
+//
+// Work is laid out per (request, kv head). The query rows of that pair are every
+// (new token, query head of the kv head's group) combination, so one pass over the
+// request's keys and values serves all `q_heads / kv_heads` heads that share them
+// (the reference's Metal kernel shares each K/V row the same way,
+// python/instinct/backends/metal_kernels.py:9-17,18-101). Keys and values are read straight
+// from the arena's pages through the block table, 64 keys at a time, into swizzled shared
+// memory with cp.async (double buffered); scores and the weighted sum use mma.sync
+// m16n8k16 with 32-bit accumulators and a 32-bit running softmax (max and sum per row).
+//
+// Two shapes of block, one body:
+//   * prefill: 4 warps own 16 query rows each (64 rows per block) and walk all keys;
+//   * decode : the request has one new token, its <= 16 rows are shared by the 4 warps, each
+//     warp takes a quarter of every 64-key tile, and the key range is cut into `splits`
+//     blocks whose partial results (max, sum, unnormalised output) a second kernel merges,
+//     as python/instinct/backends/metal_kernels.py:103-124 does.
+// Masking follows python/instinct/batches.py:110-113: key <= query position, and with a
+// window key > position - window.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kWarps = 4;
+constexpr int kFlashThreads = kWarps * 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct FlashParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k_arena;
+  const __nv_bfloat16* v_arena;
+  __nv_bfloat16* out;
+  const int* block_table;
+  const int* seq_q_start;
+  const int* seq_q_len;
+  const int* seq_kv_len;
+  float* partial_out;  // [tokens, q_heads, splits, head_dim]
+  float* partial_ml;   // [tokens, q_heads, splits, 2]
+  int* err;
+  int first_seq;
+  int max_pages, num_pages;
+  int q_heads, kv_heads, group;
+  int page_shift, page_mask;
+  int window;
+  int splits;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a swizzled [rows][HEAD_DIM] bf16 tile.
+template <int HEAD_DIM>
+__device__ __forceinline__ int tile_offset(int row, int chunk) {
+  return row * (HEAD_DIM * 2) + ((chunk ^ (row & 7)) << 4);
+}
+
+// Copies keys [tile_start, tile_start + 64) of one kv head into a shared-memory tile; rows
+// outside [lo, hi] are zero-filled (they may lie in pages the request no longer holds).
+template <int HEAD_DIM>
+__device__ __forceinline__ void load_tile(unsigned char* dst, const __nv_bfloat16* arena,
+                                          const int* table, const FlashParams& p, int kv_head,
+                                          int tile_start, int lo, int hi) {
+  constexpr int kChunks = HEAD_DIM / 8;
+  constexpr int kRowsPerPass = kFlashThreads / kChunks;
+  const int chunk = threadIdx.x % kChunks;
+  const int row0 = threadIdx.x / kChunks;
+  const int page_size = p.page_mask + 1;
+#pragma unroll
+  for (int pass = 0; pass < kTileKeys / kRowsPerPass; ++pass) {
+    const int row = row0 + pass * kRowsPerPass;
+    const int key = tile_start + row;
+    bool valid = key >= lo && key <= hi;
+    const __nv_bfloat16* src = arena;
+    if (valid) {
+      const int page = table[key >> p.page_shift];
+      if (page < 0 || page >= p.num_pages) {
+        atomicOr(p.err, ERRBIT_BAD_PAGE);
+        valid = false;
+      } else {
+        src = arena + ((static_cast<int64_t>(page) * p.kv_heads + kv_head) * page_size +
+                       (key & p.page_mask)) * HEAD_DIM + chunk * 8;
+      }
+    }
+    cp_async_16(smem_u32(dst + tile_offset<HEAD_DIM>(row, chunk)), src, valid);
+  }
+}
+
+template <int HEAD_DIM, bool DECODE>
+__global__ void __launch_bounds__(kFlashThreads)
+paged_flash_attention_kernel(const FlashParams p) {
+  constexpr int kKSteps = HEAD_DIM / 16;   // k-steps of the score product
+  constexpr int kDimTiles = HEAD_DIM / 8;  // n-tiles of the output
+  constexpr int kTileBytes = kTileKeys * HEAD_DIM * 2;
+  // Sub-blocks of 16 keys a warp handles per 64-key tile.
+  constexpr int kSubBlocks = DECODE ? 1 : kTileKeys / 16;
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* k_tiles = smem;                   // 2 stages
+  unsigned char* v_tiles = smem + 2 * kTileBytes;  // 2 stages
+
+  const int seq = p.first_seq + blockIdx.z;
+  const int kv_head = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_len = p.seq_q_len[seq];
+  const int kv_len = p.seq_kv_len[seq];
+  const int q_start = p.seq_q_start[seq];
+  const int first_pos = kv_len - q_len;  // position of the request's first new token
+  const int rows_total = q_len * p.group;
+  const int* table = p.block_table + static_cast<int64_t>(seq) * p.max_pages;
+
+  int row_base;  // first row of this warp's 16-row block
+  int split = 0;
+  if (DECODE) {
+    row_base = 0;
+    split = blockIdx.x;
+  } else {
+    row_base = blockIdx.x * (kWarps * 16) + warp * 16;
+    if (blockIdx.x * (kWarps * 16) >= rows_total) return;
+  }
+
+  // Key range this block walks.
+  int block_first_token, block_last_token;
+  if (DECODE) {
+    block_first_token = 0;
+    block_last_token = q_len - 1;
+  } else {
+    block_first_token = (blockIdx.x * (kWarps * 16)) / p.group;
+    block_last_token = min(q_len - 1, (blockIdx.x * (kWarps * 16) + kWarps * 16 - 1) / p.group);
+  }
+  int lo = p.window > 0 ? max(0, first_pos + block_first_token - p.window + 1) : 0;
+  int hi = first_pos + block_last_token;  // inclusive
+  int tile_begin = lo / kTileKeys, tile_end = hi / kTileKeys + 1;
+  if (DECODE && p.splits > 1) {
+    const int tiles = tile_end - tile_begin;
+    const int per_split = (tiles + p.splits - 1) / p.splits;
+    tile_begin = tile_begin + split * per_split;
+    tile_end = min(tile_end, tile_begin + per_split);
+  }
+  const int num_tiles = max(0, tile_end - tile_begin);
+
+  // This thread's two rows (r0 = lane / 4 and r0 + 8 of the warp's block).
+  const int r0 = row_base + (lane >> 2), r1 = r0 + 8;
+  const int tok0 = r0 / p.group, tok1 = r1 / p.group;
+  const int head0 = kv_head * p.group + (r0 - tok0 * p.group);
+  const int head1 = kv_head * p.group + (r1 - tok1 * p.group);
+  const bool live0 = r0 < rows_total, live1 = r1 < rows_total;
+  const int pos0 = first_pos + tok0, pos1 = first_pos + tok1;
+
+  // Query fragments, straight from global memory.
+  uint32_t qf[kKSteps][4];
+  {
+    const __nv_bfloat16* q0 = p.q + (static_cast<int64_t>(q_start + tok0) * p.q_heads + head0) * HEAD_DIM;
+    const __nv_bfloat16* q1 = p.q + (static_cast<int64_t>(q_start + tok1) * p.q_heads + head1) * HEAD_DIM;
+    const int col = (lane & 3) * 2;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+      qf[ks][0] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + col) : 0u;
+      qf[ks][1] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + col) : 0u;
+      qf[ks][2] = live0 ? *reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8 + col) : 0u;
+      qf[ks][3] = live1 ? *reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8 + col) : 0u;
+    }
+  }
+
+  float o[kDimTiles][4];
+#pragma unroll
+  for (int i = 0; i < kDimTiles; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  if (num_tiles > 0) {
+    load_tile<HEAD_DIM>(k_tiles, p.k_arena, table, p, kv_head, tile_begin * kTileKeys, lo, hi);
+    load_tile<HEAD_DIM>(v_tiles, p.v_arena, table, p, kv_head, tile_begin * kTileKeys, lo, hi);
+  }
+  cp_async_commit();
+
+  for (int it = 0; it < num_tiles; ++it) {
+    const int stage = it & 1;
+    const int tile_start = (tile_begin + it) * kTileKeys;
+    if (it + 1 < num_tiles) {
+      load_tile<HEAD_DIM>(k_tiles + (stage ^ 1) * kTileBytes, p.k_arena, table, p, kv_head,
+                          tile_start + kTileKeys, lo, hi);
+      load_tile<HEAD_DIM>(v_tiles + (stage ^ 1) * kTileBytes, p.v_arena, table, p, kv_head,
+                          tile_start + kTileKeys, lo, hi);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const uint32_t k_base = smem_u32(k_tiles + stage * kTileBytes);
+    const uint32_t v_base = smem_u32(v_tiles + stage * kTileBytes);
+    // Does any element of this tile need masking for this warp's rows?
+    const bool tile_needs_mask =
+        (tile_start + kTileKeys - 1 > first_pos + min(tok0, q_len - 1)) ||
+        (p.window > 0 && tile_start <= pos1 - p.window) || (tile_start < lo) || !live1;
+
+#pragma unroll
+    for (int sb = 0; sb < kSubBlocks; ++sb) {
+      const int sub = DECODE ? warp : sb;  // which 16 keys of the tile
+      const int key0 = tile_start + sub * 16;
+      if (!DECODE && key0 > hi) break;
+      // Scores of 16 rows x 16 keys: two n-tiles of 8 keys.
+      float s[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      {
+        const int mi = lane >> 3;
+        const int krow = sub * 16 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int ks = 0; ks < kKSteps; ++ks) {
+          uint32_t b[4];
+          ldmatrix_x4(b, k_base + tile_offset<HEAD_DIM>(krow, ks * 2 + (mi & 1)));
+          mma_bf16(s[0], qf[ks], b[0], b[1]);
+          mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+      }
+      // Scale, mask, running softmax. Element (n, e): row = e < 2 ? r0 : r1,
+      // key = key0 + n * 8 + (lane % 4) * 2 + (e & 1).
+      float tile_max0 = -INFINITY, tile_max1 = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[n][e] * p.scale_log2;
+          if (tile_needs_mask) {
+            const int key = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
+            const int pos = e < 2 ? pos0 : pos1;
+            const bool live = e < 2 ? live0 : live1;
+            const bool visible = live && key <= pos && key >= lo && (p.window == 0 || key > pos - p.window);
+            if (!visible) v = -INFINITY;
+          }
+          s[n][e] = v;
+          if (e < 2) tile_max0 = fmaxf(tile_max0, v);
+          else tile_max1 = fmaxf(tile_max1, v);
+        }
+      }
+      tile_max0 = fmaxf(tile_max0, __shfl_xor_sync(0xffffffffu, tile_max0, 1));
+      tile_max0 = fmaxf(tile_max0, __shfl_xor_sync(0xffffffffu, tile_max0, 2));
+      tile_max1 = fmaxf(tile_max1, __shfl_xor_sync(0xffffffffu, tile_max1, 1));
+      tile_max1 = fmaxf(tile_max1, __shfl_xor_sync(0xffffffffu, tile_max1, 2));
+      const float new0 = fmaxf(m0, tile_max0), new1 = fmaxf(m1, tile_max1);
+      const float use0 = new0 == -INFINITY ? 0.f : new0, use1 = new1 == -INFINITY ? 0.f : new1;
+      const float alpha0 = exp2f(m0 - use0), alpha1 = exp2f(m1 - use1);
+      m0 = new0;
+      m1 = new1;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pf[4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const float p00 = exp2f(s[n][0] - use0), p01 = exp2f(s[n][1] - use0);
+        const float p10 = exp2f(s[n][2] - use1), p11 = exp2f(s[n][3] - use1);
+        sum0 += p00 + p01;
+        sum1 += p10 + p11;
+        pf[n * 2 + 0] = pack_bf16(p00, p01);  // rows r0: a0/a1 (n = 0), a4/a5 (n = 1)
+        pf[n * 2 + 1] = pack_bf16(p10, p11);  // rows r1: a2/a3 (n = 0), a6/a7 (n = 1)
+      }
+      l0 = l0 * alpha0 + sum0;
+      l1 = l1 * alpha1 + sum1;
+#pragma unroll
+      for (int i = 0; i < kDimTiles; ++i) {
+        o[i][0] *= alpha0;
+        o[i][1] *= alpha0;
+        o[i][2] *= alpha1;
+        o[i][3] *= alpha1;
+      }
+      // O += P V over these 16 keys.
+      {
+        const int mi = lane >> 3;
+        const int vrow = sub * 16 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int c = 0; c < kDimTiles; c += 2) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, v_base + tile_offset<HEAD_DIM>(vrow, c + (mi >> 1)));
+          mma_bf16(o[c], pf, b[0], b[1]);
+          mma_bf16(o[c + 1], pf, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // Row sums live in the four lanes that share a row.
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  const int col = (lane & 3) * 2;
+  if (!DECODE) {
+    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    __nv_bfloat16* out0 = p.out + (static_cast<int64_t>(q_start + tok0) * p.q_heads + head0) * HEAD_DIM;
+    __nv_bfloat16* out1 = p.out + (static_cast<int64_t>(q_start + tok1) * p.q_heads + head1) * HEAD_DIM;
+#pragma unroll
+    for (int i = 0; i < kDimTiles; ++i) {
+      if (live0) *reinterpret_cast<uint32_t*>(out0 + i * 8 + col) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+      if (live1) *reinterpret_cast<uint32_t*>(out1 + i * 8 + col) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
+    return;
+  }
+
+  // Decode: merge the four warps' partial results through shared memory (the K/V tiles are
+  // no longer needed), then either finish or hand the block's partial to the merge kernel.
+  __syncthreads();
+  float* merge_o = reinterpret_cast<float*>(smem);                  // [warps][16][HEAD_DIM]
+  float* merge_ml = merge_o + kWarps * 16 * HEAD_DIM;                // [warps][16][2]
+  {
+    const int lr0 = lane >> 2, lr1 = lr0 + 8;
+#pragma unroll
+    for (int i = 0; i < kDimTiles; ++i) {
+      float* a = merge_o + (warp * 16 + lr0) * HEAD_DIM + i * 8 + col;
+      float* b = merge_o + (warp * 16 + lr1) * HEAD_DIM + i * 8 + col;
+      a[0] = o[i][0];
+      a[1] = o[i][1];
+      b[0] = o[i][2];
+      b[1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+      merge_ml[(warp * 16 + lr0) * 2 + 0] = m0;
+      merge_ml[(warp * 16 + lr0) * 2 + 1] = l0;
+      merge_ml[(warp * 16 + lr1) * 2 + 0] = m1;
+      merge_ml[(warp * 16 + lr1) * 2 + 1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int item = threadIdx.x; item < rows_total * HEAD_DIM; item += kFlashThreads) {
+    const int row = item / HEAD_DIM, d = item - row * HEAD_DIM;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+    const float use = m == -INFINITY ? 0.f : m;
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float f = exp2f(merge_ml[(w * 16 + row) * 2] - use);
+      l += merge_ml[(w * 16 + row) * 2 + 1] * f;
+      acc += merge_o[(w * 16 + row) * HEAD_DIM + d] * f;
+    }
+    const int tok = row / p.group;
+    const int head = kv_head * p.group + (row - tok * p.group);
+    const int64_t out_row = static_cast<int64_t>(q_start + tok) * p.q_heads + head;
+    if (p.splits == 1) {
+      p.out[out_row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      p.partial_out[(out_row * p.splits + split) * HEAD_DIM + d] = acc;
+      if (d == 0) {
+        p.partial_ml[(out_row * p.splits + split) * 2 + 0] = m;
+        p.partial_ml[(out_row * p.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M)
+template <int HEAD_DIM>
+__global__ void flash_merge_kernel(const float* __restrict__ partial_out,
+                                   const float* __restrict__ partial_ml,
+                                   __nv_bfloat16* __restrict__ out, int splits) {
+  const int64_t row = blockIdx.x;
+  const float* ml = partial_ml + row * splits * 2;
+  float m = -INFINITY;
+  for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i * 2]);
+  const float use = m == -INFINITY ? 0.f : m;
+  float l = 0.f;
+  for (int i = 0; i < splits; ++i) l += ml[i * 2 + 1] * exp2f(ml[i * 2] - use);
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < splits; ++i)
+      acc += partial_out[(row * splits + i) * HEAD_DIM + d] * exp2f(ml[i * 2] - use);
+    out[row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int HEAD_DIM>
+constexpr size_t flash_smem_bytes() {
+  const size_t tiles = 4 * static_cast<size_t>(kTileKeys) * HEAD_DIM * 2;
+  const size_t merge = static_cast<size_t>(kWarps) * 16 * (HEAD_DIM + 2) * sizeof(float);
+  return tiles > merge ? tiles : merge;
+}
+
+template <int HEAD_DIM>
+int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, int tokens,
+                 cudaStream_t stream) {
+  const size_t smem = flash_smem_bytes<HEAD_DIM>();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t a = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t b = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (a != cudaSuccess || b != cudaSuccess) return b200_fail("flash attention: cannot size shared memory");
+    configured = true;
+  }
+  if (decode) {
+    const dim3 grid(p.splits, p.kv_heads, num_seqs);
+    paged_flash_attention_kernel<HEAD_DIM, true><<<grid, kFlashThreads, smem, stream>>>(p);
+    if (p.splits > 1) {
+      flash_merge_kernel<HEAD_DIM><<<tokens * p.q_heads, HEAD_DIM <= 64 ? 64 : 128, 0, stream>>>(
+          p.partial_out, p.partial_ml, p.out, p.splits);
+    }
+  } else {
+    const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
+    const dim3 grid(row_blocks, p.kv_heads, num_seqs);
+    paged_flash_attention_kernel<HEAD_DIM, false><<<grid, kFlashThreads, smem, stream>>>(p);
+  }
+  return b200_check_launch("paged_flash_attention");
+}
+
+}  // namespace
+
+// Whether the tuned kernel takes this shape; the caller uses the plain kernel otherwise.
+B200_API int b200_flash_attention_supported(int q_heads, int kv_heads, int head_dim, int page_size,
+                                            int decode) {
+  if (head_dim != 64 && head_dim != 128) return 0;
+  if (q_heads % kv_heads) return 0;
+  if (page_size <= 0 || (page_size & (page_size - 1))) return 0;
+  if (decode && q_heads / kv_heads > 16) return 0;
+  if (kv_heads > 65535) return 0;
+  return 1;
+}
+
+// Scratch floats the decode form needs for `tokens` rows cut into `splits`.
+B200_API int64_t b200_flash_attention_scratch_floats(int tokens, int q_heads, int head_dim, int splits) {
+  return splits > 1 ? static_cast<int64_t>(tokens) * q_heads * splits * (head_dim + 2) : 0;
+}
+
+// Attention for requests [first_seq, first_seq + num_seqs) of the step. With `decode` each of
+// them has exactly one new token and `tokens` = num_seqs; `scratch` holds the partial
+// results when splits > 1. Query and output rows are indexed by the step's token rows.
+B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, const void* v_arena,
+                                        void* out, const int* block_table, const int* seq_q_start,
+                                        const int* seq_q_len, const int* seq_kv_len, int first_seq,
+                                        int num_seqs, int tokens, int max_q_len, int max_pages,
+                                        int num_pages, int q_heads, int kv_heads, int head_dim,
+                                        int page_size, int window, float scale, int decode, int splits,
+                                        float* scratch, int* err, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  B200_REQUIRE(b200_flash_attention_supported(q_heads, kv_heads, head_dim, page_size, decode),
+               "paged_flash_attention: unsupported shape (heads %d/%d, head_dim %d, page %d)", q_heads,
+               kv_heads, head_dim, page_size);
+  B200_REQUIRE(num_seqs > 0 && num_seqs <= 65535 && splits >= 1 && max_q_len >= 1,
+               "paged_flash_attention: bad batch");
+  B200_REQUIRE(splits == 1 || (decode && scratch != nullptr), "paged_flash_attention: splits need scratch");
+  FlashParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_arena = static_cast<const __nv_bfloat16*>(k_arena);
+  p.v_arena = static_cast<const __nv_bfloat16*>(v_arena);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_table = block_table;
+  p.seq_q_start = seq_q_start;
+  p.seq_q_len = seq_q_len;
+  p.seq_kv_len = seq_kv_len;
+  p.first_seq = first_seq;
+  p.max_pages = max_pages;
+  p.num_pages = num_pages;
+  p.q_heads = q_heads;
+  p.kv_heads = kv_heads;
+  p.group = q_heads / kv_heads;
+  int shift = 0;
+  while ((1 << shift) < page_size) ++shift;
+  p.page_shift = shift;
+  p.page_mask = page_size - 1;
+  p.window = window;
+  p.splits = decode ? splits : 1;
+  p.scale_log2 = scale * kLog2e;
+  p.err = err;
+  p.partial_out = scratch;
+  p.partial_ml = scratch ? scratch + static_cast<int64_t>(tokens) * q_heads * p.splits * head_dim : nullptr;
+  if (head_dim == 64) return launch_flash<64>(p, num_seqs, decode, max_q_len, tokens, stream);
+  return launch_flash<128>(p, num_seqs, decode, max_q_len, tokens, stream);
+}
