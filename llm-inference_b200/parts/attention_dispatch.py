@@ -1,5 +1,10 @@
-"""Chooses the attention kernel for a step: tuned kernels where their shape rules hold,
-the plain kernel otherwise (and always in float32)."""
+"""Chooses the attention kernel for a step.
+
+In bfloat16, with a head size and page size the tensor-core kernel takes, the step's
+single-token requests (which lead the batch) go to its split-key decode form and the prompt
+portions to its prefill form. Everything else - float32, other head sizes, pages whose size
+is no power of two - runs the plain kernel, which takes every shape.
+"""
 
 from __future__ import annotations
 
@@ -19,4 +24,29 @@ def attend(
     head_dim: int,
     scale: float,
 ) -> None:
-    ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale)
+    choice = ctx.options.get("attention", "auto")
+    tuned = (
+        choice != "plain"
+        and q.dtype == torch.bfloat16
+        and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=False)
+    )
+    if not tuned:
+        if choice == "flash":
+            raise ops.KernelError("the tensor-core attention kernel does not take this shape or dtype")
+        ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale)
+        return
+    decode_seqs = ctx.num_decode_seqs
+    if decode_seqs and not ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=True):
+        decode_seqs = 0  # more than 16 query heads per kv head: the prefill form handles one-token runs too
+    if decode_seqs:
+        reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
+        splits = ops.decode_splits(decode_seqs, kv_heads, reach)
+        ops.paged_flash_attention(
+            ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
+            first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits,
+        )
+    if ctx.num_seqs > decode_seqs:
+        ops.paged_flash_attention(
+            ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
+            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len,
+        )

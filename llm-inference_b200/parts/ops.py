@@ -178,6 +178,55 @@ def paged_attention_plain(
     return out
 
 
+NUM_SMS = 148
+
+
+def flash_attention_supported(ctx: StepContext, q_heads: int, kv_heads: int, head_dim: int, page_size: int, decode: bool) -> bool:
+    return bool(ctx.lib.lib.b200_flash_attention_supported(q_heads, kv_heads, head_dim, page_size, 1 if decode else 0))
+
+
+def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int) -> int:
+    """How many blocks cut each request's keys so that a decode step fills the GPU."""
+    tiles = max(1, (max_kv_len + 63) // 64)
+    want = -(-2 * NUM_SMS // max(1, num_seqs * kv_heads))
+    return max(1, min(want, tiles))
+
+
+def paged_flash_attention(
+    ctx: StepContext,
+    cache: CacheView,
+    q: torch.Tensor,
+    out: torch.Tensor,
+    q_heads: int,
+    kv_heads: int,
+    head_dim: int,
+    scale: float,
+    *,
+    first_seq: int,
+    num_seqs: int,
+    decode: bool,
+    max_q_len: int,
+    splits: int = 1,
+) -> torch.Tensor:
+    """Tensor-core attention for requests ``first_seq .. first_seq + num_seqs`` of the step."""
+    if num_seqs <= 0:
+        return out
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "flash attention is bfloat16 only")
+    _need(q.is_contiguous() and out.is_contiguous(), "flash attention: operands must be contiguous")
+    _need(not decode or first_seq == 0, "flash attention: decoded tokens must lead the batch")
+    scratch = None
+    if decode and splits > 1:
+        scratch = ctx.buffer("attention_partials", (num_seqs * q_heads * splits * (head_dim + 2),), torch.float32, per_token=False)
+    ctx.lib.call(
+        "b200_paged_flash_attention", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
+        ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs),
+        c_int(num_seqs if decode else ctx.num_tokens), c_int(max_q_len), c_int(cache.max_pages), c_int(cache.num_pages),
+        c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale),
+        c_int(1 if decode else 0), c_int(splits), ptr(scratch), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
 def _offset(tensor: torch.Tensor, nbytes: int):
     from ctypes import c_void_p
 

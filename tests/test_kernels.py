@@ -29,13 +29,14 @@ def lib():
     return kernels()
 
 
-def make_ctx(lib, token_ids=None, positions=None, token_seq=None):
+def make_ctx(lib, token_ids=None, positions=None, token_seq=None, starts=None, runs=None):
     from llm_inference_b200.parts.context import Workspace
 
     dev = torch.device("cuda:0")
     n = len(positions) if positions is not None else len(token_ids)
     as_dev = lambda v: torch.tensor(v, dtype=torch.int32, device=dev) if v is not None else None
-    return SimpleNamespace(
+    workspace = Workspace(dev)
+    ctx = SimpleNamespace(
         lib=lib,
         device=dev,
         num_tokens=n,
@@ -44,8 +45,23 @@ def make_ctx(lib, token_ids=None, positions=None, token_seq=None):
         token_seq=as_dev(token_seq),
         err=torch.zeros(1, dtype=torch.int32, device=dev),
         stream=c_void_p(torch.cuda.current_stream().cuda_stream),
-        workspace=Workspace(dev),
+        workspace=workspace,
+        options={},
+        buffer=lambda name, shape, dtype=None, per_token=True: workspace.get(name, shape, dtype, per_token=per_token),
     )
+    if runs is not None:
+        q_start = np.concatenate([[0], np.cumsum(runs)[:-1]]).tolist()
+        ctx.num_seqs = len(runs)
+        ctx.seq_q_start = as_dev(q_start)
+        ctx.seq_q_len = as_dev(list(runs))
+        ctx.seq_kv_len = as_dev([s + r for s, r in zip(starts, runs)])
+        ctx.max_q_len = max(runs)
+        ctx.max_kv_len = max(s + r for s, r in zip(starts, runs))
+        lead = 0
+        while lead < len(runs) and runs[lead] == 1:
+            lead += 1
+        ctx.num_decode_seqs = lead
+    return ctx
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -328,6 +344,91 @@ def test_window_edge_is_exact(lib):
     ops.paged_attention_plain(ctx, view, q, out, 1, 1, head_dim, 1.0)
     visible = list(range(pos - window + 1, pos + 1))
     assert abs(out[0, 0].item() - sum(visible) / len(visible)) < 1e-4
+
+
+FLASH_CASES = [
+    # q_heads, kv_heads, head_dim, page, window, starts, runs   (single-token requests lead)
+    (12, 2, 128, 64, 0, [2047, 300, 0, 63, 64, 700], [1, 1, 1, 1, 1, 1]),
+    (12, 2, 128, 16, 0, [300, 5, 0, 17], [1, 1, 70, 130]),
+    (28, 4, 128, 64, 0, [1000, 0], [1, 200]),
+    (40, 8, 128, 32, 0, [129, 64, 63], [1, 3, 2]),
+    (4, 2, 64, 8, 0, [40, 0, 7], [1, 9, 5]),
+    (6, 1, 64, 8, 24, [100, 23, 24, 0, 190], [1, 1, 1, 30, 40]),
+    (16, 1, 64, 128, 0, [500, 3], [1, 20]),
+    (8, 8, 128, 16, 100, [333, 90, 0], [1, 1, 260]),
+    (64, 2, 64, 16, 0, [77, 0], [1, 5]),  # 32 heads per kv head: single tokens take the prefill form
+]
+
+
+@pytest.mark.parametrize("case", FLASH_CASES)
+def test_paged_flash_attention(lib, case):
+    """The tensor-core kernel, both forms, through the dispatcher the model uses."""
+    from llm_inference_b200.parts import attention_dispatch, ops
+    from llm_inference_b200.parts.context import CacheView
+
+    q_heads, kv_heads, head_dim, page, window, starts, runs = case
+    q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+        torch.bfloat16, q_heads, kv_heads, head_dim, page, window, starts, runs, seed=11
+    )
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
+    ctx.options["attention"] = "flash"
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+    out = torch.full_like(q, float("nan"))
+    attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, head_dim, head_dim**-0.5)
+    assert int(ctx.err.item()) == 0
+    torch.testing.assert_close(out.double(), expected, **tol(torch.bfloat16))
+    # The same step with every request through the prefill form, and with forced splitting.
+    ctx.num_decode_seqs = 0
+    out2 = torch.full_like(q, float("nan"))
+    attention_dispatch.attend(ctx, view, q, out2, q_heads, kv_heads, head_dim, head_dim**-0.5)
+    torch.testing.assert_close(out2.double(), expected, **tol(torch.bfloat16))
+    lead = 0
+    while lead < len(runs) and runs[lead] == 1:
+        lead += 1
+    if lead and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, page, True):
+        for splits in (1, 3, 40):
+            out3 = torch.full_like(q, float("nan"))
+            ops.paged_flash_attention(ctx, view, q, out3, q_heads, kv_heads, head_dim, head_dim**-0.5,
+                                      first_seq=0, num_seqs=lead, decode=True, max_q_len=1, splits=splits)
+            torch.testing.assert_close(out3[:lead].double(), expected[:lead], **tol(torch.bfloat16))
+    assert int(ctx.err.item()) == 0
+
+
+def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(lib):
+    from llm_inference_b200.parts import attention_dispatch
+    from llm_inference_b200.parts.context import CacheView
+
+    starts, runs = [700, 0], [1, 70]
+    q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+        torch.bfloat16, 4, 2, 64, 16, 0, starts, runs, spike=(0, 17, 0)
+    )
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
+    ctx.options["attention"] = "flash"
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], 16)
+    out = torch.empty_like(q)
+    attention_dispatch.attend(ctx, view, q, out, 4, 2, 64, 64**-0.5)
+    assert expected[0].abs().min() > 9.0
+    torch.testing.assert_close(out.double(), expected, **tol(torch.bfloat16))
+    # Window edge: values encode their position, queries are zero, so the output is the mean
+    # of the visible positions.
+    head_dim, page, window = 64, 8, 24
+    for starts, runs in (([60], [1]), ([40], [30])):
+        total = starts[0] + runs[0]
+        tables, num_pages = paged_layout([total], page)
+        keys = torch.zeros(num_pages, 1, page, head_dim, device="cuda", dtype=torch.bfloat16)
+        values = torch.zeros_like(keys)
+        for p in range(total):
+            values[int(tables[0, p // page]), 0, p % page, 0] = float(p)
+        positions = list(range(starts[0], total))
+        q = torch.zeros(runs[0], head_dim, device="cuda", dtype=torch.bfloat16)
+        ctx = make_ctx(lib, positions=positions, token_seq=[0] * runs[0], starts=starts, runs=runs)
+        ctx.options["attention"] = "flash"
+        view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+        out = torch.empty_like(q)
+        attention_dispatch.attend(ctx, view, q, out, 1, 1, head_dim, 1.0)
+        for row, pos in enumerate(positions):
+            visible = list(range(max(0, pos - window + 1), pos + 1))
+            assert abs(out[row, 0].item() - sum(visible) / len(visible)) < 0.3, (pos, out[row, 0].item())
 
 
 def test_argmax_rows_takes_the_lowest_index_on_ties(lib):
