@@ -91,18 +91,37 @@ B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void
   return b200_check_launch("rmsnorm");
 }
 
-// out[t, i] = silu(gu[t, i]) * gu[t, inter + i],  silu(g) = g / (1 + exp(-g))
-// (python/instinct/backends/dense.py:124-128; cuda/kernels.cu:100-106).
+// out[t, i] = silu(gate[t, i]) * up[t, i],  silu(g) = g / (1 + exp(-g))
+// (python/instinct/backends/dense.py:124-128; cuda/kernels.cu:100-106). The input row holds
+// gate and up interleaved: gu[t, 2i] is gate_i and gu[t, 2i + 1] is up_i, which is how the
+// feed-forward stores its fused gate/up matrix.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
-                                int64_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
-  const int64_t t = idx / inter;
-  const int i = static_cast<int>(idx - t * inter);
-  const float g = to_f32<T>(gu[t * 2 * inter + i]);
-  const float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+  const float g = to_f32<T>(gu[2 * idx]);
+  const float u = to_f32<T>(gu[2 * idx + 1]);
   out[idx] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+// bfloat16, eight outputs per thread: two 16-byte loads, one 16-byte store.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                       int64_t groups) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= groups) return;
+  const uint4* src = reinterpret_cast<const uint4*>(gu) + 2 * idx;
+  const uint4 lo = src[0], hi = src[1];
+  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
+  __nv_bfloat16 r[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 p = __bfloat1622float2(a[i]);
+    const float2 q = __bfloat1622float2(b[i]);
+    r[i] = __float2bfloat16_rn(p.x / (1.f + expf(-p.x)) * p.y);
+    r[4 + i] = __float2bfloat16_rn(q.x / (1.f + expf(-q.x)) * q.y);
+  }
+  reinterpret_cast<uint4*>(out)[idx] = *reinterpret_cast<const uint4*>(r);
 }
 
 B200_API int b200_silu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype,
@@ -111,13 +130,23 @@ B200_API int b200_silu_mul(const void* gate_up, void* out, int tokens, int inter
   B200_REQUIRE(tokens > 0 && inter > 0, "silu_mul: bad sizes");
   const int64_t total = static_cast<int64_t>(tokens) * inter;
   const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   if (dtype == DTYPE_F32) {
+    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
     silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up),
-                                                          static_cast<float*>(out), inter, total);
+                                                          static_cast<float*>(out), total);
   } else if (dtype == DTYPE_BF16) {
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), inter, total);
+    const bool vec = total % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(out) % 16 == 0;
+    if (vec) {
+      const int64_t groups = total / 8;
+      const unsigned blocks = static_cast<unsigned>((groups + threads - 1) / threads);
+      silu_mul_bf16x8_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up),
+                                                             static_cast<__nv_bfloat16*>(out), groups);
+    } else {
+      const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+      silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total);
+    }
   } else {
     return b200_fail("silu_mul: unknown dtype %d", dtype);
   }

@@ -12,7 +12,9 @@ from .context import StepContext
 
 class SwiGLU(Part):
     """``down(silu(gate(h)) * up(h))`` without biases (python/instinct/backends/dense.py:124-128).
-    The gate and up matrices are stored as one ``[2 * intermediate, hidden]`` matrix."""
+    The gate and up matrices are stored as one ``[2 * intermediate, hidden]`` matrix with their
+    rows interleaved (row 2j is gate_j, row 2j + 1 is up_j), so one matrix product yields each
+    gate next to its up value and the activation can run in that product's epilogue."""
 
     def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int) -> None:
         self.prefix, self.hidden_size, self.intermediate_size = prefix, hidden_size, intermediate_size
@@ -28,9 +30,8 @@ class SwiGLU(Part):
 
     def load(self, tensors, dtype, device) -> None:
         p = self.prefix
-        self.w_gate_up = torch.cat(
-            [tensors[f"{p}{n}.weight"].to(device=device, dtype=dtype) for n in ("gate_proj", "up_proj")]
-        ).contiguous()
+        gate, up = (tensors[f"{p}{n}.weight"].to(device=device, dtype=dtype) for n in ("gate_proj", "up_proj"))
+        self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size).contiguous()
         self.w_down = tensors[f"{p}down_proj.weight"].to(device=device, dtype=dtype).contiguous()
 
     def weight_bytes(self) -> int:
@@ -38,8 +39,10 @@ class SwiGLU(Part):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         t, i = ctx.num_tokens, self.intermediate_size
-        gate_up = ops.linear(ctx, h, self.w_gate_up, ctx.buffer("gate_up", (t, 2 * i)))
-        act = ops.silu_mul(ctx, gate_up, ctx.buffer("act", (t, i)))
+        act = ctx.buffer("act", (t, i))
+        if not ops.linear_swiglu(ctx, h, self.w_gate_up, act):
+            gate_up = ops.linear(ctx, h, self.w_gate_up, ctx.buffer("gate_up", (t, 2 * i)))
+            ops.silu_mul(ctx, gate_up, act)
         return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
 
 

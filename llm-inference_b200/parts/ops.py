@@ -64,6 +64,10 @@ def linear(
         )
         return out
     _need(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: bfloat16 path needs bfloat16 operands")
+    if bias is None and _use_skinny(ctx, m, n, k, 0):
+        epilogue = 1 if out.dtype == torch.float32 else 0
+        ctx.lib.call("b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue), ctx.stream)
+        return out
     if out.dtype == torch.float32:
         _need(bias is None, "linear: no bias on the 32-bit output path")
         _mm_f32_out(x, weight, out)
@@ -72,6 +76,25 @@ def linear(
     else:
         torch.mm(x, weight.t(), out=out)
     return out
+
+
+def _use_skinny(ctx: StepContext, m: int, n: int, k: int, epilogue: int) -> bool:
+    """Few rows: stream the weights through this engine's own kernel instead of the library."""
+    if ctx.options.get("gemm", "auto") == "library":
+        return False
+    return bool(ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue))
+
+
+def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """``out = silu(gate) * up`` of ``x @ weight.T`` with interleaved gate/up rows, in one
+    kernel. Returns False (doing nothing) when the fused kernel does not take the shape."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if x.dtype != torch.bfloat16 or m == 0 or not _use_skinny(ctx, m, n, k, 2):
+        return False
+    _need(tuple(out.shape) == (m, n // 2) and out.is_contiguous() and x.is_contiguous(), "linear_swiglu: bad operands")
+    ctx.lib.call("b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(2), ctx.stream)
+    return True
 
 
 def embedding_gather(ctx: StepContext, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

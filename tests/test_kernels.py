@@ -145,8 +145,48 @@ def test_silu_mul(lib, dtype):
     gate_up = (torch.randn(13, 2 * 272, device="cuda") * 4).to(dtype)
     out = torch.empty(13, 272, device="cuda", dtype=dtype)
     ops.silu_mul(make_ctx(lib, positions=[0] * 13), gate_up, out)
-    g, u = gate_up[:, :272].double(), gate_up[:, 272:].double()
+    g, u = gate_up[:, 0::2].double(), gate_up[:, 1::2].double()  # gate and up interleaved
     torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+    odd = (torch.randn(3, 2 * 37, device="cuda") * 4).to(dtype)  # not a multiple of eight
+    out = torch.empty(3, 37, device="cuda", dtype=dtype)
+    ops.silu_mul(make_ctx(lib, positions=[0] * 3), odd, out)
+    g, u = odd[:, 0::2].double(), odd[:, 1::2].double()
+    torch.testing.assert_close(out.double(), g / (1 + torch.exp(-g)) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize(
+    "m,n,k",
+    [(1, 2048, 1536), (8, 1536, 8960), (5, 311, 96), (64, 272, 96), (17, 100, 64), (33, 4608, 3584), (8, 50, 40),
+     (2, 3000, 264), (64, 151936, 64)],
+)
+def test_skinny_gemm_matches_float64(lib, m, n, k):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(m * 7 + n)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    ctx = make_ctx(lib, positions=[0] * m)
+    want = x.double() @ w.double().T
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
+        ops.linear(ctx, x, w, out)
+        kw = dict(atol=2e-2, rtol=2e-2) if out_dtype == torch.bfloat16 else dict(atol=1e-4, rtol=1e-4)
+        torch.testing.assert_close(out.double(), want, **kw)
+    # Against the library product of the same operands.
+    ctx.options["gemm"] = "library"
+    ref = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    ops.linear(ctx, x, w, ref)
+    ctx.options["gemm"] = "auto"
+    torch.testing.assert_close(out, ref, atol=2e-4, rtol=2e-4)
+    # A row's result does not depend on the other rows of the call.
+    alone = torch.empty(1, n, device="cuda", dtype=torch.float32)
+    ops.linear(ctx, x[m - 1 :].contiguous(), w, alone)
+    assert torch.equal(alone[0], out[m - 1])
+    if n % 2 == 0:
+        act = torch.full((m, n // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+        assert ops.linear_swiglu(ctx, x, w, act)
+        g, u = want[:, 0::2], want[:, 1::2]
+        torch.testing.assert_close(act.double(), g / (1 + torch.exp(-g)) * u, atol=2e-2, rtol=2e-2)
 
 
 def paged_layout(seq_lens, page_size, extra_pages=3, seed=0):
