@@ -1,0 +1,162 @@
+"""Times one kernel of the library alone, at a given shape, with CUDA events.
+
+    python -m llm_inference_b200.cli.microbench gemm --m 8 --n 17920 --k 1536 [--swiglu] [--library]
+    python -m llm_inference_b200.cli.microbench decode_attention --batch 64 --context 2048
+    python -m llm_inference_b200.cli.microbench prefill_attention --tokens 2048
+
+Between timed launches a buffer larger than the L2 cache is overwritten, so every launch
+reads its operands from HBM. Prints one JSON line with the median time and the bytes or flops
+per second it corresponds to. Used for roofline numbers and as the small case for profiler
+captures.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+from ctypes import c_void_p
+from types import SimpleNamespace
+
+import numpy as np
+import torch
+
+
+class _Ctx(SimpleNamespace):
+    @property
+    def stream(self):
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def make_ctx(positions=None, token_seq=None, starts=None, runs=None, options=None):
+    from ..csrc.library import kernels
+    from ..parts.context import Workspace
+
+    dev = torch.device("cuda:0")
+    ws = Workspace(dev)
+    as_dev = lambda v: torch.tensor(v, dtype=torch.int32, device=dev) if v is not None else None
+    ctx = _Ctx(
+        lib=kernels(), device=dev, err=torch.zeros(1, dtype=torch.int32, device=dev), workspace=ws,
+        options=dict(options or {}), positions=as_dev(positions), token_seq=as_dev(token_seq),
+        num_tokens=len(positions) if positions is not None else 0,
+        buffer=lambda name, shape, dtype=None, per_token=True: ws.get(name, shape, dtype, per_token=per_token),
+    )
+    if runs is not None:
+        ctx.num_seqs = len(runs)
+        ctx.seq_q_start = as_dev(np.concatenate([[0], np.cumsum(runs)[:-1]]).tolist())
+        ctx.seq_q_len = as_dev(list(runs))
+        ctx.seq_kv_len = as_dev([s + r for s, r in zip(starts, runs)])
+        ctx.max_q_len = max(runs)
+        ctx.max_kv_len = max(s + r for s, r in zip(starts, runs))
+        ctx.num_decode_seqs = len(runs) if max(runs) == 1 else 0
+    return ctx
+
+
+def time_launches(fn, iters: int, warmup: int = 3) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def bench_gemm(args) -> dict:
+    from ..parts import ops
+
+    m, n, k = args.m, args.n, args.k
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") / k**0.5).to(torch.bfloat16)
+    ctx = make_ctx(positions=[0] * m, options={"gemm": "library" if args.library else "auto"})
+    if args.swiglu:
+        out = torch.empty(m, n // 2, device="cuda", dtype=torch.bfloat16)
+        if args.library:
+            mid = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+
+            def fn():
+                ops.linear(ctx, x, w, mid)
+                ops.silu_mul(ctx, mid, out)
+        else:
+            fn = lambda: ops.linear_swiglu(ctx, x, w, out)
+    else:
+        out = torch.empty(m, n, device="cuda", dtype=torch.float32 if args.f32_out else torch.bfloat16)
+        fn = lambda: ops.linear(ctx, x, w, out)
+    us = time_launches(fn, args.iters)
+    nbytes = w.numel() * 2 + x.numel() * 2 + out.numel() * out.element_size()
+    return {"kernel": "gemm", "m": m, "n": n, "k": k, "library": args.library, "swiglu": args.swiglu, "us": us,
+            "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * m * n * k / us / 1e6}
+
+
+def bench_attention(args, decode: bool) -> dict:
+    from ..parts import attention_dispatch
+    from ..parts.context import CacheView
+
+    q_heads, kv_heads, dim, page = args.q_heads, args.kv_heads, args.head_dim, args.page
+    if decode:
+        starts, runs = [args.context - 1] * args.batch, [1] * args.batch
+    else:
+        starts, runs = [args.context - args.tokens], [args.tokens]
+    lens = [s + r for s, r in zip(starts, runs)]
+    need = [-(-n // page) for n in lens]
+    num_pages = sum(need) + 1
+    order = np.random.default_rng(0).permutation(num_pages - 1)
+    tables = np.zeros((len(lens), max(need)), dtype=np.int32)
+    at = 0
+    for s, c in enumerate(need):
+        tables[s, :c] = order[at : at + c]
+        at += c
+    keys = torch.randn(num_pages, kv_heads, page, dim, device="cuda").to(torch.bfloat16)
+    values = torch.randn_like(keys)
+    positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
+    token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
+    ctx = make_ctx(positions, token_seq, starts, runs, {"attention": "plain" if args.plain else "auto"})
+    q = torch.randn(len(positions), q_heads * dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, args.window)
+    fn = lambda: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5)
+    us = time_launches(fn, args.iters)
+    kv_bytes = sum(lens) * kv_heads * dim * 2 * 2
+    flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs))
+    return {"kernel": "decode_attention" if decode else "prefill_attention", "batch": len(lens), "context": args.context,
+            "tokens": len(positions), "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention"])
+    parser.add_argument("--m", type=int, default=8)
+    parser.add_argument("--n", type=int, default=17920)
+    parser.add_argument("--k", type=int, default=1536)
+    parser.add_argument("--swiglu", action="store_true")
+    parser.add_argument("--f32-out", action="store_true")
+    parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=2048)
+    parser.add_argument("--tokens", type=int, default=2048)
+    parser.add_argument("--q-heads", type=int, default=12)
+    parser.add_argument("--kv-heads", type=int, default=2)
+    parser.add_argument("--head-dim", type=int, default=128)
+    parser.add_argument("--page", type=int, default=64)
+    parser.add_argument("--window", type=int, default=0)
+    parser.add_argument("--plain", action="store_true")
+    parser.add_argument("--iters", type=int, default=20)
+    args = parser.parse_args(argv)
+    if args.kernel == "gemm":
+        result = bench_gemm(args)
+    else:
+        result = bench_attention(args, args.kernel == "decode_attention")
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

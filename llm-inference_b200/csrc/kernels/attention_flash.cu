@@ -135,6 +135,8 @@ paged_flash_attention_kernel(const FlashParams p) {
   unsigned char* k_tiles = smem;                   // 2 stages
   unsigned char* v_tiles = smem + 2 * kTileBytes;  // 2 stages
 
+  wait_for_predecessor();
+  let_successor_start();
   const int seq = p.first_seq + blockIdx.z;
   const int kv_head = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -391,6 +393,8 @@ template <int HEAD_DIM>
 __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
                                    const float* __restrict__ partial_ml,
                                    __nv_bfloat16* __restrict__ out, int splits) {
+  wait_for_predecessor();
+  let_successor_start();
   const int64_t row = blockIdx.x;
   const float* ml = partial_ml + row * splits * 2;
   float m = -INFINITY;
@@ -429,15 +433,15 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
   }
   if (decode) {
     const dim3 grid(p.splits, p.kv_heads, num_seqs);
-    paged_flash_attention_kernel<HEAD_DIM, true><<<grid, kFlashThreads, smem, stream>>>(p);
+    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
-      flash_merge_kernel<HEAD_DIM><<<tokens * p.q_heads, HEAD_DIM <= 64 ? 64 : 128, 0, stream>>>(
-          p.partial_out, p.partial_ml, p.out, p.splits);
+      launch_kernel(flash_merge_kernel<HEAD_DIM>, dim3(tokens * p.q_heads), dim3(HEAD_DIM <= 64 ? 64 : 128), 0,
+                    stream, p.partial_out, p.partial_ml, p.out, p.splits);
     }
   } else {
     const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
     const dim3 grid(row_blocks, p.kv_heads, num_seqs);
-    paged_flash_attention_kernel<HEAD_DIM, false><<<grid, kFlashThreads, smem, stream>>>(p);
+    launch_kernel(paged_flash_attention_kernel<HEAD_DIM, false>, grid, dim3(kFlashThreads), smem, stream, p);
   }
   return b200_check_launch("paged_flash_attention");
 }

@@ -18,6 +18,14 @@ int b200_check_launch(const char* what) {
   return 0;
 }
 
+static bool g_overlap = true;
+
+bool b200_overlap_enabled() { return g_overlap; }
+
+// Switches programmatic dependent launch (kernels overlapping their predecessor's tail) on or
+// off for every later launch of this library.
+B200_API void b200_set_overlap(int enabled) { g_overlap = enabled != 0; }
+
 B200_API const char* b200_last_error() { return g_error; }
 
 B200_API int b200_abi_version() { return 1; }

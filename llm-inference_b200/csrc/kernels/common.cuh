@@ -32,6 +32,33 @@ int b200_check_launch(const char* what);
     if (!(cond)) return b200_fail(__VA_ARGS__); \
   } while (0)
 
+// Programmatic dependent launch. A kernel launched through `launch_kernel` with overlap
+// enabled may start while its predecessor on the stream is still running; it must call
+// `wait_for_predecessor()` before it reads anything the predecessor wrote or writes anything
+// at all, and may read constants (weights) before that. `let_successor_start()` tells the
+// scheduler that the next kernel on the stream may be made resident as soon as there is
+// room. In a kernel launched the ordinary way both calls do nothing.
+__device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_successor_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool b200_overlap_enabled();
+
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = b200_overlap_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

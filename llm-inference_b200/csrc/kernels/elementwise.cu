@@ -9,6 +9,8 @@ template <typename T>
 __global__ void embedding_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                         float* __restrict__ out, int hidden, int vocab,
                                         int* __restrict__ err) {
+  wait_for_predecessor();
+  let_successor_start();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + static_cast<int64_t>(t) * hidden;
@@ -28,11 +30,11 @@ B200_API int b200_embedding_gather(const void* table, int table_dtype, const int
   B200_REQUIRE(tokens > 0 && hidden > 0 && vocab > 0, "embedding_gather: bad sizes");
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == DTYPE_F32) {
-    embedding_gather_kernel<float><<<tokens, threads, 0, stream>>>(
-        static_cast<const float*>(table), ids, out, hidden, vocab, err);
+    launch_kernel(embedding_gather_kernel<float>, dim3(tokens), dim3(threads), 0, stream,
+                  static_cast<const float*>(table), ids, out, hidden, vocab, err);
   } else if (table_dtype == DTYPE_BF16) {
-    embedding_gather_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, err);
+    launch_kernel(embedding_gather_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                  static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab, err);
   } else {
     return b200_fail("embedding_gather: unknown dtype %d", table_dtype);
   }
@@ -50,6 +52,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
                                const float* __restrict__ weight, T* __restrict__ out,
                                const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
+  wait_for_predecessor();
+  let_successor_start();
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* xr = x + static_cast<int64_t>(r) * hidden;
   const T* dr = delta ? delta + static_cast<int64_t>(r) * hidden : nullptr;
@@ -79,12 +83,12 @@ B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void
   B200_REQUIRE(num_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (dtype == DTYPE_F32) {
-    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>(
-        x, static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
+    launch_kernel(rmsnorm_kernel<float>, dim3(num_rows), dim3(threads), 0, stream, x,
+                  static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);
   } else if (dtype == DTYPE_BF16) {
-    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>(
-        x, static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out),
-        rows, hidden, eps);
+    launch_kernel(rmsnorm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), 0, stream, x,
+                  static_cast<const __nv_bfloat16*>(delta), weight, static_cast<__nv_bfloat16*>(out), rows,
+                  hidden, eps);
   } else {
     return b200_fail("rmsnorm: unknown dtype %d", dtype);
   }
@@ -97,6 +101,8 @@ B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void
 // feed-forward stores its fused gate/up matrix.
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total) {
+  wait_for_predecessor();
+  let_successor_start();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const float g = to_f32<T>(gu[2 * idx]);
@@ -107,6 +113,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 // bfloat16, eight outputs per thread: two 16-byte loads, one 16-byte store.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                                        int64_t groups) {
+  wait_for_predecessor();
+  let_successor_start();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= groups) return;
   const uint4* src = reinterpret_cast<const uint4*>(gu) + 2 * idx;
@@ -132,20 +140,20 @@ B200_API int b200_silu_mul(const void* gate_up, void* out, int tokens, int inter
   const int threads = 256;
   if (dtype == DTYPE_F32) {
     const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(static_cast<const float*>(gate_up),
-                                                          static_cast<float*>(out), total);
+    launch_kernel(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream,
+                  static_cast<const float*>(gate_up), static_cast<float*>(out), total);
   } else if (dtype == DTYPE_BF16) {
     const bool vec = total % 8 == 0 && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
                      reinterpret_cast<uintptr_t>(out) % 16 == 0;
     if (vec) {
       const int64_t groups = total / 8;
       const unsigned blocks = static_cast<unsigned>((groups + threads - 1) / threads);
-      silu_mul_bf16x8_kernel<<<blocks, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(gate_up),
-                                                             static_cast<__nv_bfloat16*>(out), groups);
+      launch_kernel(silu_mul_bf16x8_kernel, dim3(blocks), dim3(threads), 0, stream,
+                    static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), groups);
     } else {
       const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
-      silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-          static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total);
+      launch_kernel(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
+                    static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total);
     }
   } else {
     return b200_fail("silu_mul: unknown dtype %d", dtype);

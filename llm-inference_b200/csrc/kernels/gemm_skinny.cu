@@ -1,14 +1,21 @@
-// Matrix product for a handful of tokens (decode steps):  Y[M,N] = X[M,K] * W[N,K]^T, M <= 64.
+// Matrix product for a handful of tokens (decode steps):  Y[M,N] = X[M,K] * W[N,K]^T, M <= 16.
 //
 // With so few rows the product is a stream of the weight matrix through the GPU once, so the
 // kernel is built around that stream. The roles of the operands are swapped for the tensor
 // cores: 16 rows of W are the "A" tile of mma.sync m16n8k16 and 8 tokens are its "B" tile.
-// Each lane fetches its share of a 16 x 32 slab of W with two 16-byte loads straight from
-// global memory into fragment registers (the order of k inside a slab is permuted the same
-// way for W and X, which a dot product does not notice), several slabs ahead, so that every
-// warp keeps a few KB in flight. The 8 warps of a block are `row_groups` groups of 16 weight
+// Each lane owns its share of a 16 x 32 slab of W as two 16-byte pieces in fragment order (the
+// order of k inside a slab is permuted the same way for W and X, which a dot product does not
+// notice). The pieces travel global -> shared memory with cp.async into a private ring of
+// `kStages` slabs per warp, so every warp keeps kStages KB in flight without holding them in
+// registers, and a lane reads back only what it fetched itself (no barriers in the loop).
+// The weights of the first slabs are requested before the kernel waits for its predecessor
+// on the stream, so their latency hides behind the previous kernel's tail.
+// The 8 warps of a block are `row_groups` groups of 16 weight
 // rows times `k_splits` slices of K; the slices' partial sums meet in shared memory and are
-// added in slice order, so the result does not depend on timing. Linear layers are x W^T with
+// added in slice order, so the result does not depend on timing. When W has too few rows to
+// give every SM a block, several blocks share a column of rows and split K among them: each
+// writes its sums to scratch memory and the one that finishes last adds them in block order.
+// Linear layers are x W^T with
 // W stored [out, in] (python/instinct/backends/base.py:83-101); the reference sends them to
 // cuBLASLt (cuda/execution_context.cu:95-110).
 //
@@ -21,8 +28,8 @@ namespace {
 
 constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
-constexpr int kChunk = 32;  // k per slab
-constexpr int kAhead = 4;   // slabs fetched ahead per warp
+constexpr int kChunk = 32;   // k per slab
+constexpr int kStages = 8;   // slabs in flight per warp
 
 enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
@@ -35,76 +42,110 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 load_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
+__device__ __forceinline__ void copy_async_16(void* dst, const void* src, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int bytes = valid ? 16 : 0;  // zero-fills when not valid
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// Sum of the k-slices' partial results for output (row r, token m) of this block, in slice order.
+__device__ __forceinline__ float block_sum_at(const float* partial, int k_splits, int block_rows,
+                                              int tokens_pad, int r, int m) {
+  float sum = 0.f;
+  for (int s = 0; s < k_splits; ++s) sum += partial[(static_cast<int64_t>(s) * block_rows + r) * tokens_pad + m];
+  return sum;
 }
 
 template <int MT>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
-                   void* __restrict__ Y, int M, int N, int K, int row_groups, int epilogue) {
-  extern __shared__ float partial[];  // [k_splits][row_groups * 16][MT * 8]
+                   void* __restrict__ Y, int M, int N, int K, int row_groups, int epilogue,
+                   float* __restrict__ scratch, int* __restrict__ counters) {
+  // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* ring = reinterpret_cast<uint4*>(smem_raw);
+  __shared__ int ticket_shared;
+  constexpr int kPieces = 2 + MT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int k_splits = kSkinnyWarps / row_groups;
   const int rg = warp % row_groups, ks = warp / row_groups;
   const int block_rows = row_groups * 16;
   const int n0 = blockIdx.x * block_rows + rg * 16;
+  uint4* my_ring = ring + static_cast<int64_t>(warp) * kStages * kPieces * 32;
 
+  // K is cut first across the blocks of a column (gridDim.y), then across this block's warps.
   const int chunks = (K + kChunk - 1) / kChunk;
-  const int per_split = (chunks + k_splits - 1) / k_splits;
-  const int c_begin = ks * per_split, c_end = min(chunks, c_begin + per_split);
+  const int per_block = (chunks + gridDim.y - 1) / gridDim.y;
+  const int b_begin = blockIdx.y * per_block, b_end = min(chunks, b_begin + per_block);
+  const int per_split = (max(0, b_end - b_begin) + k_splits - 1) / k_splits;
+  const int c_begin = b_begin + ks * per_split, c_end = min(b_end, c_begin + per_split);
 
   const int row_a = n0 + g, row_b = n0 + g + 8;
   const bool live_a = row_a < N, live_b = row_b < N;
   const __nv_bfloat16* wa = W + static_cast<int64_t>(live_a ? row_a : 0) * K + t * 8;
   const __nv_bfloat16* wb = W + static_cast<int64_t>(live_b ? row_b : 0) * K + t * 8;
 
+  auto fetch_w = [&](int c, int stage) {
+    const bool in = c < c_end && c * kChunk + t * 8 < K;
+    uint4* slot = my_ring + stage * kPieces * 32;
+    copy_async_16(slot + lane, wa + (in ? c * kChunk : 0), in && live_a);
+    copy_async_16(slot + 32 + lane, wb + (in ? c * kChunk : 0), in && live_b);
+  };
+  auto fetch_x = [&](int c, int stage) {
+    const bool in = c < c_end && c * kChunk + t * 8 < K;
+    uint4* slot = my_ring + stage * kPieces * 32;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const bool live = mt * 8 + g < M;
+      const __nv_bfloat16* x = X + static_cast<int64_t>(live ? mt * 8 + g : 0) * K + t * 8;
+      copy_async_16(slot + (2 + mt) * 32 + lane, x + (in ? c * kChunk : 0), in && live);
+    }
+  };
+
+  // Weights do not depend on the previous kernel: request them first, then wait for it.
+#pragma unroll
+  for (int i = 0; i < kStages; ++i) fetch_w(c_begin + i, i);
+  copy_async_commit();
+  wait_for_predecessor();
+  let_successor_start();
+#pragma unroll
+  for (int i = 0; i < kStages; ++i) fetch_x(c_begin + i, i);
+  copy_async_commit();
+  copy_async_wait<0>();
+
   float acc[MT][4];
 #pragma unroll
   for (int i = 0; i < MT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  uint4 fa[kAhead], fb[kAhead];
+  int stage = 0;
+  for (int c = c_begin; c < c_end; ++c) {
+    // Every iteration commits one group, so all but the newest kStages - 1 are complete here.
+    copy_async_wait<kStages - 1>();
+    const uint4* slot = my_ring + stage * kPieces * 32;
+    const uint4 a = slot[lane], b = slot[32 + lane];
 #pragma unroll
-  for (int i = 0; i < kAhead; ++i) {
-    const int c = c_begin + i;
-    const bool in = c < c_end && c * kChunk + t * 8 < K;
-    fa[i] = (in && live_a) ? load_stream(wa + c * kChunk) : zero;
-    fb[i] = (in && live_b) ? load_stream(wb + c * kChunk) : zero;
-  }
-
-  for (int c0 = c_begin; c0 < c_end; c0 += kAhead) {
-#pragma unroll
-    for (int i = 0; i < kAhead; ++i) {
-      const int c = c0 + i;
-      if (c >= c_end) break;
-      const uint4 a = fa[i], b = fb[i];
-      // Refill this slot with the slab kAhead further on.
-      {
-        const int cn = c + kAhead;
-        const bool in = cn < c_end && cn * kChunk + t * 8 < K;
-        fa[i] = (in && live_a) ? load_stream(wa + cn * kChunk) : zero;
-        fb[i] = (in && live_b) ? load_stream(wb + cn * kChunk) : zero;
-      }
-      const bool k_in = c * kChunk + t * 8 < K;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int token = mt * 8 + g;
-        uint4 x = zero;
-        if (token < M && k_in)
-          x = __ldg(reinterpret_cast<const uint4*>(X + static_cast<int64_t>(token) * K + c * kChunk + t * 8));
-        mma_bf16_16816(acc[mt], a.x, b.x, a.y, b.y, x.x, x.y);
-        mma_bf16_16816(acc[mt], a.z, b.z, a.w, b.w, x.z, x.w);
-      }
+    for (int mt = 0; mt < MT; ++mt) {
+      const uint4 x = slot[(2 + mt) * 32 + lane];
+      mma_bf16_16816(acc[mt], a.x, b.x, a.y, b.y, x.x, x.y);
+      mma_bf16_16816(acc[mt], a.z, b.z, a.w, b.w, x.z, x.w);
     }
+    // The pieces are in registers and used; refill the slot with the slab kStages further on.
+    fetch_w(c + kStages, stage);
+    fetch_x(c + kStages, stage);
+    copy_async_commit();
+    stage = stage + 1 == kStages ? 0 : stage + 1;
   }
+  copy_async_wait<0>();
+  __syncthreads();  // the ring is reused for the partial sums below
 
   // Partial sums of this warp: rows (rg * 16 + g, + 8), tokens mt * 8 + 2t, + 1.
+  float* partial = reinterpret_cast<float*>(smem_raw);  // [k_splits][block_rows][MT * 8]
   const int tokens_pad = MT * 8;
   float* mine = partial + (static_cast<int64_t>(ks) * block_rows + rg * 16) * tokens_pad;
 #pragma unroll
@@ -116,18 +157,40 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
   }
   __syncthreads();
 
+  const int tile = block_rows * tokens_pad;
+  const float* sums = nullptr;  // when set: [gridDim.y][tile] partials of every block of this column
+  if (gridDim.y > 1) {
+    // Hand this block's sums to the column's scratch; the block that arrives last adds all of
+    // them in block order, so the result does not depend on which block that is.
+    float* column = scratch + static_cast<int64_t>(blockIdx.x) * gridDim.y * tile;
+    for (int item = threadIdx.x; item < tile; item += kSkinnyThreads)
+      column[static_cast<int64_t>(blockIdx.y) * tile + item] =
+          block_sum_at(partial, k_splits, block_rows, tokens_pad, item / tokens_pad, item % tokens_pad);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_shared = atomicAdd(&counters[blockIdx.x], 1);
+    __syncthreads();
+    if (ticket_shared != static_cast<int>(gridDim.y) - 1) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[blockIdx.x] = 0;  // ready for the next launch
+    sums = column;
+  }
+
   const int block_n0 = blockIdx.x * block_rows;
+  auto total = [&](int r, int m) -> float {
+    if (sums == nullptr) return block_sum_at(partial, k_splits, block_rows, tokens_pad, r, m);
+    float sum = 0.f;
+    for (int s = 0; s < static_cast<int>(gridDim.y); ++s)
+      sum += __ldcg(sums + static_cast<int64_t>(s) * tile + r * tokens_pad + m);
+    return sum;
+  };
   if (epilogue == EPI_SWIGLU) {
     const int pairs = block_rows / 2;
     for (int item = threadIdx.x; item < M * pairs; item += kSkinnyThreads) {
       const int m = item / pairs, j = item - m * pairs;
       const int n = block_n0 + 2 * j;
       if (n >= N) continue;
-      float gate = 0.f, up = 0.f;
-      for (int s = 0; s < k_splits; ++s) {
-        gate += partial[(static_cast<int64_t>(s) * block_rows + 2 * j) * tokens_pad + m];
-        up += partial[(static_cast<int64_t>(s) * block_rows + 2 * j + 1) * tokens_pad + m];
-      }
+      const float gate = total(2 * j, m), up = total(2 * j + 1, m);
       static_cast<__nv_bfloat16*>(Y)[static_cast<int64_t>(m) * (N / 2) + n / 2] =
           __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
     }
@@ -136,50 +199,99 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       const int m = item / block_rows, r = item - m * block_rows;
       const int n = block_n0 + r;
       if (n >= N) continue;
-      float sum = 0.f;
-      for (int s = 0; s < k_splits; ++s) sum += partial[(static_cast<int64_t>(s) * block_rows + r) * tokens_pad + m];
+      const float sum = total(r, m);
       if (epilogue == EPI_F32) static_cast<float*>(Y)[static_cast<int64_t>(m) * N + n] = sum;
       else static_cast<__nv_bfloat16*>(Y)[static_cast<int64_t>(m) * N + n] = __float2bfloat16_rn(sum);
     }
   }
 }
 
+// How the launcher cuts the work; a function of N and K only, so that a token's sums are added
+// in the same order whatever else is in the batch. The aim is one wave of long-lived warps:
+// about two blocks per SM, each warp streaming a contiguous run of slabs.
+struct SkinnyPlan {
+  int row_groups;
+  int column_blocks;  // blocks that share one column of W rows and split K
+  int blocks;
+};
+
+SkinnyPlan plan_skinny(int N, int K) {
+  const int tiles = (N + 15) / 16;
+  const int chunks = (K + kChunk - 1) / kChunk;
+  const int wave = 2 * 148 * kSkinnyWarps;
+  int slices = (wave + tiles / 2) / tiles;            // K slices per 16 rows, over all blocks
+  slices = max(1, min(slices, max(1, chunks / 6)));  // every warp keeps a few slabs to stream
+  int k_splits = 1;
+  while (k_splits < kSkinnyWarps && k_splits < slices) k_splits *= 2;
+  SkinnyPlan plan;
+  plan.row_groups = kSkinnyWarps / k_splits;
+  plan.column_blocks = max(1, min(8, (slices + k_splits - 1) / k_splits));
+  const int block_rows = plan.row_groups * 16;
+  plan.blocks = (N + block_rows - 1) / block_rows;
+  return plan;
+}
+
 template <int MT>
 int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
-                  int row_groups, int epilogue, cudaStream_t stream) {
-  const int block_rows = row_groups * 16;
-  const int blocks = (N + block_rows - 1) / block_rows;
-  const int k_splits = kSkinnyWarps / row_groups;
-  const size_t smem = static_cast<size_t>(k_splits) * block_rows * MT * 8 * sizeof(float);
-  skinny_gemm_kernel<MT><<<blocks, kSkinnyThreads, smem, stream>>>(W, X, Y, M, N, K, row_groups, epilogue);
-  return b200_check_launch("skinny_gemm");
+                  const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream) {
+  const int block_rows = plan.row_groups * 16;
+  const int k_splits = kSkinnyWarps / plan.row_groups;
+  const size_t ring = static_cast<size_t>(kSkinnyWarps) * kStages * (2 + MT) * 32 * 16;
+  const size_t sums = static_cast<size_t>(k_splits) * block_rows * MT * 8 * sizeof(float);
+  const size_t smem = ring > sums ? ring : sums;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(skinny_gemm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return b200_fail("skinny_gemm: cannot size shared memory");
+    configured = true;
+  }
+  const dim3 grid(plan.blocks, plan.column_blocks);
+  cudaError_t status = launch_kernel(skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X, Y, M,
+                                     N, K, plan.row_groups, epilogue, scratch, counters);
+  if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
+  return 0;
 }
 
 }  // namespace
 
-// Shapes the kernel takes: at most 64 rows, K a multiple of 8 (16-byte rows), 16-byte aligned
+constexpr int kSkinnyMaxRows = 16;
+
+// Shapes the kernel takes: at most 16 rows, K a multiple of 8 (16-byte rows), 16-byte aligned
 // operands; for the SwiGLU epilogue N even.
 B200_API int b200_skinny_gemm_supported(int M, int N, int K, int epilogue) {
-  if (M < 1 || M > 64 || N < 1 || K < 8 || K % 8) return 0;
+  if (M < 1 || M > kSkinnyMaxRows || N < 1 || K < 8 || K % 8) return 0;
   if (epilogue == EPI_SWIGLU && N % 2) return 0;
   return 1;
 }
 
+// Scratch the product needs when blocks share a column: `floats` 32-bit words of partial sums
+// and `counters` ints that must be zero before the first launch (each launch leaves them zero).
+B200_API void b200_skinny_gemm_scratch(int M, int N, int K, int64_t* floats, int* counters) {
+  const SkinnyPlan plan = plan_skinny(N, K);
+  const int tokens_pad = (M + 7) / 8 * 8;
+  *floats = plan.column_blocks > 1
+                ? static_cast<int64_t>(plan.blocks) * plan.column_blocks * plan.row_groups * 16 * tokens_pad
+                : 0;
+  *counters = plan.column_blocks > 1 ? plan.blocks : 0;
+}
+
 B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
+                              float* scratch, int64_t scratch_floats, int* counters, int num_counters,
                               cudaStream_t stream) {
   B200_REQUIRE(b200_skinny_gemm_supported(M, N, K, epilogue), "skinny_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "skinny_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
                "skinny_gemm: operands must be 16-byte aligned");
-  // Rows of W per block: as large as still leaves a few blocks per SM. The choice depends on
-  // N alone, so a token's sums are added in the same order whatever else is in the batch.
-  const int mt = (M + 7) / 8;
-  int row_groups = 1;
-  while (row_groups < kSkinnyWarps && (N + row_groups * 32 - 1) / (row_groups * 32) >= 3 * 148) row_groups *= 2;
+  const SkinnyPlan plan = plan_skinny(N, K);
+  int64_t need_floats;
+  int need_counters;
+  b200_skinny_gemm_scratch(M, N, K, &need_floats, &need_counters);
+  B200_REQUIRE(scratch_floats >= need_floats && num_counters >= need_counters,
+               "skinny_gemm: scratch too small (%lld floats, %d counters needed)",
+               static_cast<long long>(need_floats), need_counters);
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (mt <= 1) return launch_skinny<1>(w, x, Y, M, N, K, row_groups, epilogue, stream);
-  if (mt <= 2) return launch_skinny<2>(w, x, Y, M, N, K, row_groups, epilogue, stream);
-  if (mt <= 4) return launch_skinny<4>(w, x, Y, M, N, K, row_groups, epilogue, stream);
-  return launch_skinny<8>(w, x, Y, M, N, K, row_groups, epilogue, stream);
+  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
 }

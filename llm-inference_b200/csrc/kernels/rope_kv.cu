@@ -19,6 +19,8 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      int kv_heads, int head_dim, int rot, int page_size,
                                      int write_kv, int* __restrict__ err) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
+  wait_for_predecessor();
+  let_successor_start();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half_rot = rot / 2;
@@ -115,12 +117,12 @@ B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float*
   const int threads = 128;
   const size_t smem = sizeof(float) * (rot > 0 ? rot : 2);
   if (dtype == DTYPE_F32) {
-    rope_kv_write_kernel<float><<<tokens, threads, smem, stream>>>(
+    launch_kernel(rope_kv_write_kernel<float>, dim3(tokens), dim3(threads), smem, stream,
         static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, block_table,
         max_pages, num_pages, static_cast<float*>(k_arena), static_cast<float*>(v_arena),
         static_cast<float*>(q_out), q_heads, kv_heads, head_dim, rot, page_size, write_kv, err);
   } else if (dtype == DTYPE_BF16) {
-    rope_kv_write_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
+    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream,
         static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, block_table,
         max_pages, num_pages, static_cast<__nv_bfloat16*>(k_arena),
         static_cast<__nv_bfloat16*>(v_arena), static_cast<__nv_bfloat16*>(q_out), q_heads,

@@ -34,6 +34,8 @@ argmax_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stri
                    const int* __restrict__ row_index, int* __restrict__ out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  wait_for_predecessor();
+  let_successor_start();
   const int src_row = row_index ? row_index[blockIdx.x] : blockIdx.x;
   const float* row = logits + src_row * row_stride;
   float bv = -INFINITY;
@@ -142,6 +144,8 @@ sample_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stri
   __shared__ float partial[kSampleThreads];
   __shared__ int chosen;
 
+  wait_for_predecessor();
+  let_successor_start();
   const int r = blockIdx.x;
   const int src_row = row_index ? row_index[r] : r;
   const float* row = logits + src_row * row_stride;
@@ -248,8 +252,8 @@ B200_API int b200_argmax_rows(const float* logits, int rows, int vocab, int64_t 
                               const int* row_index, int* out, cudaStream_t stream) {
   if (rows == 0) return 0;
   B200_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "argmax_rows: bad sizes");
-  argmax_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, row_stride, row_index,
-                                                          out);
+  launch_kernel(argmax_rows_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, logits, vocab, row_stride,
+                row_index, out);
   return b200_check_launch("argmax_rows");
 }
 
@@ -262,7 +266,7 @@ B200_API int b200_sample_rows(const float* logits, int rows, int vocab, int64_t 
                               const int* row_index, int* out, cudaStream_t stream) {
   if (rows == 0) return 0;
   B200_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "sample_rows: bad sizes");
-  sample_rows_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, row_stride, temperature,
-                                                          top_p, min_p, top_k, keys, row_index, out);
+  launch_kernel(sample_rows_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, logits, vocab, row_stride,
+                temperature, top_p, min_p, top_k, keys, row_index, out);
   return b200_check_launch("sample_rows");
 }

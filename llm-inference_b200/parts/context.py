@@ -74,6 +74,16 @@ class Workspace:
             self.generation += 1
         return flat[:count].view(shape)
 
+    def zeros(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
+        """A buffer that starts zeroed and whose users leave it zeroed (arrival counters)."""
+        key = f"{name}:{dtype}:zeros"
+        flat = self._flat.get(key)
+        if flat is None or flat.numel() < count:
+            flat = torch.zeros(count, dtype=dtype, device=self.device)
+            self._flat[key] = flat
+            self.generation += 1
+        return flat
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())
 

@@ -65,8 +65,7 @@ def linear(
         return out
     _need(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: bfloat16 path needs bfloat16 operands")
     if bias is None and _use_skinny(ctx, m, n, k, 0):
-        epilogue = 1 if out.dtype == torch.float32 else 0
-        ctx.lib.call("b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue), ctx.stream)
+        _skinny(ctx, x, weight, out, 1 if out.dtype == torch.float32 else 0)
         return out
     if out.dtype == torch.float32:
         _need(bias is None, "linear: no bias on the 32-bit output path")
@@ -93,8 +92,36 @@ def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: 
     if x.dtype != torch.bfloat16 or m == 0 or not _use_skinny(ctx, m, n, k, 2):
         return False
     _need(tuple(out.shape) == (m, n // 2) and out.is_contiguous() and x.is_contiguous(), "linear_swiglu: bad operands")
-    ctx.lib.call("b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(2), ctx.stream)
+    _skinny(ctx, x, weight, out, 2)
     return True
+
+
+_SKINNY_SCRATCH: dict[tuple[int, int, int], tuple[int, int]] = {}
+
+
+def _skinny(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
+    """Launch the weight-streaming product; its scratch (partial sums of blocks that share a
+    column, and their arrival counters) lives in the step's workspace."""
+    from ctypes import byref
+
+    m, k = x.shape
+    n = weight.shape[0]
+    key = ((m + 7) // 8, n, k)
+    need = _SKINNY_SCRATCH.get(key)
+    if need is None:
+        floats, counters = c_int64(0), c_int(0)
+        ctx.lib.lib.b200_skinny_gemm_scratch(m, n, k, byref(floats), byref(counters))
+        need = _SKINNY_SCRATCH[key] = (floats.value, counters.value)
+    floats, counters = need
+    scratch = counter_buf = None
+    if floats:
+        scratch = ctx.buffer("gemm_partials", (floats,), torch.float32, per_token=False)
+        counter_buf = ctx.workspace.zeros("gemm_counters", max(counters, 4096), torch.int32)
+    ctx.lib.call(
+        "b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue),
+        ptr(scratch), c_int64(floats), ptr(counter_buf), c_int(counter_buf.numel() if counter_buf is not None else 0),
+        ctx.stream,
+    )
 
 
 def embedding_gather(ctx: StepContext, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
