@@ -1,0 +1,424 @@
+// Weight-streaming matrix product on the 5th-generation tensor cores:
+//   Y[M,N] = X[M,K] * W[N,K]^T  for up to 256 rows of X (decode steps and short portions).
+//
+// The operands swap roles so the weights fill the tensor core's wide side: a block owns 128
+// rows of W (the MMA's M) and all tokens (the MMA's N, padded to a multiple of 16). One
+// thread feeds a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte
+// swizzle): a 128 x 64 tile of W and a tokens x 64 tile of X per stage. One thread issues
+// tcgen05.mma (cta_group::1, kind::f16, bf16 in, fp32 accumulate) from those stages into a
+// TMEM accumulator of 128 lanes x tokens columns and releases each stage with
+// tcgen05.commit. Four warps read the accumulator back with tcgen05.ld and write Y.
+// The weight tiles of the first stages are requested before the kernel waits for its
+// predecessor on the stream (programmatic dependent launch), since weights never depend on it.
+//
+// When W has too few rows to give every SM a block, blocks that share rows split K; each
+// writes its partial tile to scratch and the one that finishes last adds them in block
+// order, so the sum does not depend on timing.
+//
+// Every wait on an mbarrier is bounded: on a timeout the block records ERRBIT_TIMEOUT in the
+// error word, stops issuing work, frees its TMEM and returns.
+//
+// Linear layers are x W^T with W stored [out, in] (python/instinct/backends/base.py:83-101);
+// the reference sends them to cuBLASLt (cuda/execution_context.cu:95-110). Epilogues as in
+// gemm_skinny.cu: bfloat16 or float32 rows, or SwiGLU over interleaved gate/up rows
+// (python/instinct/backends/dense.py:124-128).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBlockRows = 128;  // rows of W per block = MMA M
+constexpr int kBlockK = 64;      // k per stage: 128 bytes of bf16 = one swizzle row
+constexpr int kMmaK = 16;
+constexpr int kStagesT = 4;      // 18 KB each at 16 tokens: three blocks fit an SM and overlap their ramps
+constexpr int kThreadsT = 192;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
+constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
+constexpr int ERRBIT_TIMEOUT = 8;
+
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+// Bounded wait for the phase with the given parity to complete.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_addr(bar);
+  const long long start = clock64();
+  while (true) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (clock64() - start > kWaitCycles) return false;
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);   // start address
+  desc |= static_cast<uint64_t>(1) << 16;                  // leading byte offset (unused for swizzled K-major)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;                  // descriptor version (sm_100)
+  desc |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
+  return desc;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(kBlockRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct StreamParams {
+  void* y;
+  float* scratch;
+  int* counters;
+  int* err;
+  int M, N, K;
+  int tokens_pad;  // MMA N: M rounded up to a multiple of 16
+  int tmem_cols;   // power of two >= max(32, tokens_pad)
+  int epilogue;
+};
+
+__global__ void __launch_bounds__(kThreadsT)
+stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
+                   const StreamParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // Stage s: W tile (128 x 128 B) then X tile (tokens_pad x 128 B), each 1024-byte aligned.
+  const uint32_t w_bytes = kBlockRows * kBlockK * 2;
+  const uint32_t x_bytes = static_cast<uint32_t>(p.tokens_pad) * kBlockK * 2;
+  const uint32_t x_stride = (x_bytes + 1023u) & ~1023u;
+  const uint32_t stage_bytes = w_bytes + x_stride;
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full_bar[kStagesT];
+  __shared__ __align__(8) uint64_t empty_bar[kStagesT];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_shared;
+  __shared__ int ticket_shared;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBlockRows;
+  const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  const int per_block = (k_blocks + gridDim.y - 1) / gridDim.y;
+  const int kb_begin = blockIdx.y * per_block;
+  const int kb_end = min(k_blocks, kb_begin + per_block);
+  const int num_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesT; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_shared)),
+                 "r"(static_cast<uint32_t>(p.tmem_cols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_shared;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer -----------------------------------------------------------------------
+    // Weights of the first stages go out before the dependency wait; X follows it.
+    const int first = min(num_kb, kStagesT);
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full_bar[i], w_bytes + x_bytes);
+      tma_load_2d(tiles + i * stage_bytes, &w_map, &full_bar[i], (kb_begin + i) * kBlockK, n0);
+    }
+    wait_for_predecessor();
+    let_successor_start();
+    for (int i = 0; i < first; ++i)
+      tma_load_2d(tiles + i * stage_bytes + w_bytes, &x_map, &full_bar[i], (kb_begin + i) * kBlockK, 0);
+    for (int i = first; i < num_kb; ++i) {
+      const int s = i % kStagesT;
+      const uint32_t parity = ((i / kStagesT) - 1) & 1;
+      if (!mbar_wait(&empty_bar[s], parity)) {
+        atomicOr(p.err, ERRBIT_TIMEOUT);
+        break;
+      }
+      mbar_expect_tx(&full_bar[s], w_bytes + x_bytes);
+      tma_load_2d(tiles + s * stage_bytes, &w_map, &full_bar[s], (kb_begin + i) * kBlockK, n0);
+      tma_load_2d(tiles + s * stage_bytes + w_bytes, &x_map, &full_bar[s], (kb_begin + i) * kBlockK, 0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer -------------------------------------------------------------------------
+    wait_for_predecessor();
+    const uint32_t idesc = umma_instr_desc(p.tokens_pad);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % kStagesT;
+      if (!mbar_wait(&full_bar[s], (i / kStagesT) & 1)) {
+        atomicOr(p.err, ERRBIT_TIMEOUT);
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_addr(tiles + s * stage_bytes);
+      const uint32_t b_addr = a_addr + w_bytes;
+#pragma unroll
+      for (int k = 0; k < kBlockK / kMmaK; ++k) {
+        const uint64_t a_desc = umma_smem_desc(a_addr + k * kMmaK * 2);
+        const uint64_t b_desc = umma_smem_desc(b_addr + k * kMmaK * 2);
+        umma_bf16(tmem_base, a_desc, b_desc, idesc, i > 0 || k > 0);
+      }
+      umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+    }
+    umma_commit(&accum_bar);  // the accumulator is complete once every MMA has retired
+  } else if (warp >= 2) {
+    // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
+    wait_for_predecessor();
+    const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
+    const int row = quarter * 32 + lane;
+    const int n = n0 + row;
+    bool ok = true;
+    if (num_kb > 0) {
+      ok = mbar_wait(&accum_bar, 0);
+      if (!ok && lane == 0) atomicOr(p.err, ERRBIT_TIMEOUT);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int tile = kBlockRows * p.tokens_pad;
+    float* column = p.scratch ? p.scratch + static_cast<int64_t>(blockIdx.x) * gridDim.y * tile : nullptr;
+    // Pass 1 (only when K is split): park this block's partial tile, laid out [token][row].
+    if (gridDim.y > 1) {
+      for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
+        float v[16];
+        if (ok && num_kb > 0) {
+          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          column[static_cast<int64_t>(blockIdx.y) * tile + (c0 + i) * kBlockRows + row] = v[i];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (warp == 2 && lane == 0) ticket_shared = atomicAdd(&p.counters[blockIdx.x], 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool last = ticket_shared == static_cast<int>(gridDim.y) - 1;
+      if (last) {
+        __threadfence();
+        if (warp == 2 && lane == 0) p.counters[blockIdx.x] = 0;  // ready for the next launch
+      } else {
+        ok = false;  // somebody else finishes this column
+      }
+    }
+    if (ok || (gridDim.y > 1 && ticket_shared == static_cast<int>(gridDim.y) - 1)) {
+      for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
+        float v[16];
+        if (gridDim.y > 1) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float sum = 0.f;
+            for (int s = 0; s < static_cast<int>(gridDim.y); ++s)
+              sum += __ldcg(column + static_cast<int64_t>(s) * tile + (c0 + i) * kBlockRows + row);
+            v[i] = sum;
+          }
+        } else if (num_kb > 0) {
+          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        if (p.epilogue == EPI_SWIGLU) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float up = __shfl_down_sync(0xffffffffu, v[i], 1);
+            const int m = c0 + i;
+            if ((lane & 1) == 0 && m < p.M && n < p.N) {
+              const float gate = v[i];
+              static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
+                  __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = c0 + i;
+            if (m < p.M && n < p.N) {
+              if (p.epilogue == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v[i];
+              else static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(p.tmem_cols))
+                 : "memory");
+  }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult status;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &status) == cudaSuccess &&
+        status == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(ptr);
+  }
+  return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix as a 2-D tensor map with boxes of 64 k x box_rows rows.
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return b200_fail("stream_gemm: the driver does not provide cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {kBlockK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult status =
+      encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (status != CUDA_SUCCESS) return b200_fail("stream_gemm: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(status));
+  return 0;
+}
+
+struct StreamPlan {
+  int blocks;
+  int column_blocks;
+};
+
+// A function of N and K only (see gemm_skinny.cu): about one block per SM.
+StreamPlan plan_stream(int N, int K) {
+  StreamPlan plan;
+  plan.blocks = (N + kBlockRows - 1) / kBlockRows;
+  const int k_blocks = (K + kBlockK - 1) / kBlockK;
+  int column = max(1, min(16, 148 / plan.blocks));
+  while (column > 1 && k_blocks / column < 3) --column;  // every block keeps a few stages to stream
+  plan.column_blocks = column;
+  return plan;
+}
+
+}  // namespace
+
+constexpr int kStreamMaxRows = 256;
+
+// Shapes the kernel takes: at most 256 rows of X, K a multiple of 8 (row pitch a multiple of 16
+// bytes, which TMA needs), N even for the SwiGLU epilogue.
+B200_API int b200_stream_gemm_supported(int M, int N, int K, int epilogue) {
+  if (M < 1 || M > kStreamMaxRows || N < 1 || K < 8 || K % 8) return 0;
+  if (epilogue == EPI_SWIGLU && N % 2) return 0;
+  return 1;
+}
+
+B200_API void b200_stream_gemm_scratch(int M, int N, int K, int64_t* floats, int* counters) {
+  const StreamPlan plan = plan_stream(N, K);
+  const int tokens_pad = (M + 15) / 16 * 16;
+  *floats = plan.column_blocks > 1 ? static_cast<int64_t>(plan.blocks) * plan.column_blocks * kBlockRows * tokens_pad : 0;
+  *counters = plan.column_blocks > 1 ? plan.blocks : 0;
+}
+
+B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
+                              float* scratch, int64_t scratch_floats, int* counters, int num_counters, int* err,
+                              cudaStream_t stream) {
+  B200_REQUIRE(b200_stream_gemm_supported(M, N, K, epilogue), "stream_gemm: unsupported shape %d x %d x %d", M, N, K);
+  B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
+               "stream_gemm: operands must be 16-byte aligned");
+  const StreamPlan plan = plan_stream(N, K);
+  int64_t need_floats;
+  int need_counters;
+  b200_stream_gemm_scratch(M, N, K, &need_floats, &need_counters);
+  B200_REQUIRE(scratch_floats >= need_floats && num_counters >= need_counters,
+               "stream_gemm: scratch too small (%lld floats, %d counters needed)",
+               static_cast<long long>(need_floats), need_counters);
+  StreamParams p;
+  p.y = Y;
+  p.scratch = need_floats ? scratch : nullptr;
+  p.counters = counters;
+  p.err = err;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.tokens_pad = (M + 15) / 16 * 16;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < p.tokens_pad) p.tmem_cols *= 2;
+  p.epilogue = epilogue;
+  CUtensorMap w_map, x_map;
+  if (make_map(&w_map, W, N, K, kBlockRows) != 0) return -1;
+  if (make_map(&x_map, X, M, K, p.tokens_pad) != 0) return -1;
+  const size_t x_stride = (static_cast<size_t>(p.tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
+  const size_t smem = kStagesT * (static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride) + 1024;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", smem);
+    configured = smem;
+  }
+  const dim3 grid(plan.blocks, plan.column_blocks);
+  const cudaError_t status = launch_kernel(stream_gemm_kernel, grid, dim3(kThreadsT), smem, stream, w_map, x_map, p);
+  if (status != cudaSuccess) return b200_fail("stream_gemm: %s", cudaGetErrorString(status));
+  return 0;
+}

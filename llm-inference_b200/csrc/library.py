@@ -21,6 +21,7 @@ ERROR_BITS = {
     1: "a block-table entry was negative or past the cache arena",
     2: "a token id was outside the embedding table",
     4: "a position did not fit the block table",
+    8: "a kernel gave up waiting on one of its own barriers",
 }
 
 
@@ -57,6 +58,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
     "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p],
+    "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p],
     "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p],
     "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p],
 }
@@ -74,6 +76,10 @@ class KernelLibrary:
         self.lib.b200_skinny_gemm_supported.restype = c_int
         self.lib.b200_skinny_gemm_scratch.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]
         self.lib.b200_skinny_gemm_scratch.restype = None
+        self.lib.b200_stream_gemm_supported.argtypes = [c_int] * 4
+        self.lib.b200_stream_gemm_supported.restype = c_int
+        self.lib.b200_stream_gemm_scratch.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]
+        self.lib.b200_stream_gemm_scratch.restype = None
         self._functions = {}
         self.calls = 0  # kernel launches issued through this library
         for name, argtypes in _SIGNATURES.items():

@@ -64,9 +64,12 @@ def linear(
         )
         return out
     _need(x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16, "linear: bfloat16 path needs bfloat16 operands")
-    if bias is None and _use_skinny(ctx, m, n, k, 0):
-        _skinny(ctx, x, weight, out, 1 if out.dtype == torch.float32 else 0)
-        return out
+    if bias is None:
+        epilogue = 1 if out.dtype == torch.float32 else 0
+        kernel = _small_gemm_kernel(ctx, m, n, k, epilogue)
+        if kernel is not None:
+            _small_gemm(ctx, kernel, x, weight, out, epilogue)
+            return out
     if out.dtype == torch.float32:
         _need(bias is None, "linear: no bias on the 32-bit output path")
         _mm_f32_out(x, weight, out)
@@ -77,51 +80,64 @@ def linear(
     return out
 
 
-def _use_skinny(ctx: StepContext, m: int, n: int, k: int, epilogue: int) -> bool:
-    """Few rows: stream the weights through this engine's own kernel instead of the library."""
-    if ctx.options.get("gemm", "auto") == "library":
-        return False
-    return bool(ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue))
+def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) -> str | None:
+    """Which of this engine's own weight-streaming products takes the shape, if any.
+
+    ``options["gemm"]``: ``"auto"`` (tcgen05 kernel, else the mma.sync one), ``"tcgen05"``,
+    ``"skinny"``, or ``"library"`` (always the vendor library)."""
+    choice = ctx.options.get("gemm", "auto")
+    if choice == "library":
+        return None
+    if choice in ("auto", "tcgen05") and ctx.lib.lib.b200_stream_gemm_supported(m, n, k, epilogue):
+        return "stream"
+    if choice in ("auto", "skinny") and ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue):
+        return "skinny"
+    return None
 
 
 def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
     """``out = silu(gate) * up`` of ``x @ weight.T`` with interleaved gate/up rows, in one
-    kernel. Returns False (doing nothing) when the fused kernel does not take the shape."""
+    kernel. Returns False (doing nothing) when no fused kernel takes the shape."""
     m, k = x.shape
     n = weight.shape[0]
-    if x.dtype != torch.bfloat16 or m == 0 or not _use_skinny(ctx, m, n, k, 2):
+    if x.dtype != torch.bfloat16 or m == 0:
+        return False
+    kernel = _small_gemm_kernel(ctx, m, n, k, 2)
+    if kernel is None:
         return False
     _need(tuple(out.shape) == (m, n // 2) and out.is_contiguous() and x.is_contiguous(), "linear_swiglu: bad operands")
-    _skinny(ctx, x, weight, out, 2)
+    _small_gemm(ctx, kernel, x, weight, out, 2)
     return True
 
 
-_SKINNY_SCRATCH: dict[tuple[int, int, int], tuple[int, int]] = {}
+_GEMM_SCRATCH: dict[tuple[str, int, int, int], tuple[int, int]] = {}
 
 
-def _skinny(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
-    """Launch the weight-streaming product; its scratch (partial sums of blocks that share a
-    column, and their arrival counters) lives in the step's workspace."""
+def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
+    """Launch a weight-streaming product; its scratch (partial sums of blocks that share
+    rows of the weight matrix, and their arrival counters) lives in the step's workspace."""
     from ctypes import byref
 
     m, k = x.shape
     n = weight.shape[0]
-    key = ((m + 7) // 8, n, k)
-    need = _SKINNY_SCRATCH.get(key)
+    key = (kernel, (m + 15) // 16, n, k)
+    need = _GEMM_SCRATCH.get(key)
     if need is None:
         floats, counters = c_int64(0), c_int(0)
-        ctx.lib.lib.b200_skinny_gemm_scratch(m, n, k, byref(floats), byref(counters))
-        need = _SKINNY_SCRATCH[key] = (floats.value, counters.value)
+        getattr(ctx.lib.lib, f"b200_{kernel}_gemm_scratch")(m, n, k, byref(floats), byref(counters))
+        need = _GEMM_SCRATCH[key] = (floats.value, counters.value)
     floats, counters = need
     scratch = counter_buf = None
     if floats:
         scratch = ctx.buffer("gemm_partials", (floats,), torch.float32, per_token=False)
         counter_buf = ctx.workspace.zeros("gemm_counters", max(counters, 4096), torch.int32)
-    ctx.lib.call(
-        "b200_skinny_gemm", ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue),
-        ptr(scratch), c_int64(floats), ptr(counter_buf), c_int(counter_buf.numel() if counter_buf is not None else 0),
-        ctx.stream,
-    )
+    args = [
+        ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue), ptr(scratch), c_int64(floats),
+        ptr(counter_buf), c_int(counter_buf.numel() if counter_buf is not None else 0),
+    ]
+    if kernel == "stream":
+        args.append(ptr(ctx.err))
+    ctx.lib.call(f"b200_{kernel}_gemm", *args, ctx.stream)
 
 
 def embedding_gather(ctx: StepContext, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

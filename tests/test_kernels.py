@@ -159,13 +159,16 @@ def test_silu_mul(lib, dtype):
     [(1, 2048, 1536), (8, 1536, 8960), (5, 311, 96), (16, 272, 96), (9, 100, 64), (13, 4608, 3584), (8, 50, 40),
      (2, 3000, 264), (16, 151936, 64), (3, 1536, 1536), (8, 3584, 18944)],
 )
-def test_skinny_gemm_matches_float64(lib, m, n, k):
+@pytest.mark.parametrize("kernel", ["skinny", "tcgen05"])
+def test_weight_streaming_gemm_matches_float64(lib, m, n, k, kernel):
     from llm_inference_b200.parts import ops
 
     torch.manual_seed(m * 7 + n)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
     ctx = make_ctx(lib, positions=[0] * m)
+    ctx.options["gemm"] = kernel
+    assert ops._small_gemm_kernel(ctx, m, n, k, 0) == {"skinny": "skinny", "tcgen05": "stream"}[kernel]
     want = x.double() @ w.double().T
     for out_dtype in (torch.bfloat16, torch.float32):
         out = torch.full((m, n), float("nan"), device="cuda", dtype=out_dtype)
@@ -176,7 +179,7 @@ def test_skinny_gemm_matches_float64(lib, m, n, k):
     ctx.options["gemm"] = "library"
     ref = torch.empty(m, n, device="cuda", dtype=torch.float32)
     ops.linear(ctx, x, w, ref)
-    ctx.options["gemm"] = "auto"
+    ctx.options["gemm"] = kernel
     torch.testing.assert_close(out, ref, atol=2e-4, rtol=2e-4)
     # A row's result does not depend on the other rows of the call.
     alone = torch.empty(1, n, device="cuda", dtype=torch.float32)
@@ -187,6 +190,27 @@ def test_skinny_gemm_matches_float64(lib, m, n, k):
         assert ops.linear_swiglu(ctx, x, w, act)
         g, u = want[:, 0::2], want[:, 1::2]
         torch.testing.assert_close(act.double(), g / (1 + torch.exp(-g)) * u, atol=2e-2, rtol=2e-2)
+    assert int(ctx.err.item()) == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 1536, 1536), (64, 17920, 1536), (100, 272, 96), (256, 2048, 1536), (33, 1536, 8960)])
+def test_tcgen05_gemm_takes_up_to_256_rows(lib, m, n, k):
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(m + n)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    ctx = make_ctx(lib, positions=[0] * m)
+    ctx.options["gemm"] = "tcgen05"
+    out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+    ops.linear(ctx, x, w, out)
+    torch.testing.assert_close(out.double(), x.double() @ w.double().T, atol=1e-4, rtol=1e-4)
+    act = torch.full((m, n // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+    assert ops.linear_swiglu(ctx, x, w, act)
+    want = x.double() @ w.double().T
+    g, u = want[:, 0::2], want[:, 1::2]
+    torch.testing.assert_close(act.double(), g / (1 + torch.exp(-g)) * u, atol=2e-2, rtol=2e-2)
+    assert int(ctx.err.item()) == 0
 
 
 def paged_layout(seq_lens, page_size, extra_pages=3, seed=0):
