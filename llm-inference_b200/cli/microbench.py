@@ -70,16 +70,53 @@ def time_launches(fn, iters: int, warmup: int = 3) -> float:
     return statistics.median(times)
 
 
+def time_back_to_back(fns, launches: int) -> float:
+    """Microseconds per launch when ``fns`` run round-robin back to back on the device. The
+    launches are captured in a CUDA graph, so host launch cost does not enter; the operands
+    of all of them together must exceed the L2 cache."""
+    for fn in fns:
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches):
+            fns[i % len(fns)]()
+    graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) * 1e3 / launches
+
+
 def bench_gemm(args) -> dict:
     from ..parts import ops
 
     m, n, k = args.m, args.n, args.k
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") / k**0.5).to(torch.bfloat16)
-    ctx = make_ctx(positions=[0] * m, options={"gemm": "library" if args.library else "auto"})
+    ctx = make_ctx(positions=[0] * m, options={"gemm": args.gemm})
+    if args.rotate:
+        # Enough copies of the weights that one round exceeds the L2 cache several times.
+        copies = max(2, -(-(512 << 20) // (w.numel() * 2)))
+        weights = [w] + [w.clone() for _ in range(copies - 1)]
+        out = torch.empty(m, n // 2 if args.swiglu else n, device="cuda", dtype=torch.float32 if args.f32_out else torch.bfloat16)
+        if args.swiglu and args.gemm == "library":
+            mid = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+            fns = [lambda wi=wi: (ops.linear(ctx, x, wi, mid), ops.silu_mul(ctx, mid, out)) for wi in weights]
+        elif args.swiglu:
+            fns = [lambda wi=wi: ops.linear_swiglu(ctx, x, wi, out) for wi in weights]
+        else:
+            fns = [lambda wi=wi: ops.linear(ctx, x, wi, out) for wi in weights]
+        us = time_back_to_back(fns, 4 * copies)
+        nbytes = w.numel() * 2 + x.numel() * 2 + out.numel() * out.element_size()
+        return {"kernel": "gemm", "m": m, "n": n, "k": k, "gemm": args.gemm, "swiglu": args.swiglu, "mode": "back-to-back",
+                "us": us, "GBps": nbytes / us / 1e3}
     if args.swiglu:
         out = torch.empty(m, n // 2, device="cuda", dtype=torch.bfloat16)
-        if args.library:
+        if args.gemm == "library":
             mid = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
 
             def fn():
@@ -92,7 +129,7 @@ def bench_gemm(args) -> dict:
         fn = lambda: ops.linear(ctx, x, w, out)
     us = time_launches(fn, args.iters)
     nbytes = w.numel() * 2 + x.numel() * 2 + out.numel() * out.element_size()
-    return {"kernel": "gemm", "m": m, "n": n, "k": k, "library": args.library, "swiglu": args.swiglu, "us": us,
+    return {"kernel": "gemm", "m": m, "n": n, "k": k, "gemm": args.gemm, "swiglu": args.swiglu, "us": us,
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * m * n * k / us / 1e6}
 
 
@@ -139,6 +176,8 @@ def main(argv=None) -> int:
     parser.add_argument("--swiglu", action="store_true")
     parser.add_argument("--f32-out", action="store_true")
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
+    parser.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "skinny", "library"])
+    parser.add_argument("--rotate", action="store_true", help="launch back to back over rotating copies of the weights")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048)
     parser.add_argument("--tokens", type=int, default=2048)
@@ -150,6 +189,8 @@ def main(argv=None) -> int:
     parser.add_argument("--plain", action="store_true")
     parser.add_argument("--iters", type=int, default=20)
     args = parser.parse_args(argv)
+    if args.library:
+        args.gemm = "library"
     if args.kernel == "gemm":
         result = bench_gemm(args)
     else:

@@ -11,9 +11,11 @@
 // The weight tiles of the first stages are requested before the kernel waits for its
 // predecessor on the stream (programmatic dependent launch), since weights never depend on it.
 //
-// When W has too few rows to give every SM a block, blocks that share rows split K; each
-// writes its partial tile to scratch and the one that finishes last adds them in block
-// order, so the sum does not depend on timing.
+// When W has too few rows to give every SM a block, the blocks that share rows form a
+// thread-block cluster and split K among them: each leaves its partial tile in its own shared
+// memory, and after a cluster barrier every block adds a slice of the rows over all members
+// in rank order through distributed shared memory, so the sum does not depend on timing and
+// no global scratch is needed.
 //
 // Every wait on an mbarrier is bounded: on a timeout the block records ERRBIT_TIMEOUT in the
 // error word, stops issuing work, frees its TMEM and returns.
@@ -24,6 +26,8 @@
 // (python/instinct/backends/dense.py:124-128).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -31,7 +35,7 @@ namespace {
 constexpr int kBlockRows = 128;  // rows of W per block = MMA M
 constexpr int kBlockK = 64;      // k per stage: 128 bytes of bf16 = one swizzle row
 constexpr int kMmaK = 16;
-constexpr int kStagesT = 4;      // 18 KB each at 16 tokens: three blocks fit an SM and overlap their ramps
+constexpr int kMaxStages = 12;    // the launcher picks the depth from how many blocks share an SM
 constexpr int kThreadsT = 192;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
 constexpr int ERRBIT_TIMEOUT = 8;
@@ -123,14 +127,29 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
 
 struct StreamParams {
   void* y;
-  float* scratch;
-  int* counters;
   int* err;
+  int stages;
   int M, N, K;
   int tokens_pad;  // MMA N: M rounded up to a multiple of 16
   int tmem_cols;   // power of two >= max(32, tokens_pad)
   int epilogue;
 };
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void write_output(const StreamParams& p, int m, int n, float v) {
+  if (p.epilogue == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v;
+  else static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(v);
+}
 
 __global__ void __launch_bounds__(kThreadsT)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
@@ -142,22 +161,23 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   const uint32_t x_stride = (x_bytes + 1023u) & ~1023u;
   const uint32_t stage_bytes = w_bytes + x_stride;
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ __align__(8) uint64_t full_bar[kStagesT];
-  __shared__ __align__(8) uint64_t empty_bar[kStagesT];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_base_shared;
-  __shared__ int ticket_shared;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = p.stages;
   const int n0 = blockIdx.x * kBlockRows;
+  const int members = gridDim.y;  // blocks of this cluster; blockIdx.y is the rank
   const int k_blocks = (p.K + kBlockK - 1) / kBlockK;
-  const int per_block = (k_blocks + gridDim.y - 1) / gridDim.y;
+  const int per_block = (k_blocks + members - 1) / members;
   const int kb_begin = blockIdx.y * per_block;
   const int kb_end = min(k_blocks, kb_begin + per_block);
   const int num_kb = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStagesT; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -178,7 +198,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   if (warp == 0 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------------
     // Weights of the first stages go out before the dependency wait; X follows it.
-    const int first = min(num_kb, kStagesT);
+    const int first = min(num_kb, stages);
     for (int i = 0; i < first; ++i) {
       mbar_expect_tx(&full_bar[i], w_bytes + x_bytes);
       tma_load_2d(tiles + i * stage_bytes, &w_map, &full_bar[i], (kb_begin + i) * kBlockK, n0);
@@ -188,8 +208,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     for (int i = 0; i < first; ++i)
       tma_load_2d(tiles + i * stage_bytes + w_bytes, &x_map, &full_bar[i], (kb_begin + i) * kBlockK, 0);
     for (int i = first; i < num_kb; ++i) {
-      const int s = i % kStagesT;
-      const uint32_t parity = ((i / kStagesT) - 1) & 1;
+      const int s = i % stages;
+      const uint32_t parity = ((i / stages) - 1) & 1;
       if (!mbar_wait(&empty_bar[s], parity)) {
         atomicOr(p.err, ERRBIT_TIMEOUT);
         break;
@@ -200,14 +220,11 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer -------------------------------------------------------------------------
-    wait_for_predecessor();
     const uint32_t idesc = umma_instr_desc(p.tokens_pad);
-    bool ok = true;
-    for (int i = 0; i < num_kb && ok; ++i) {
-      const int s = i % kStagesT;
-      if (!mbar_wait(&full_bar[s], (i / kStagesT) & 1)) {
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % stages;
+      if (!mbar_wait(&full_bar[s], (i / stages) & 1)) {
         atomicOr(p.err, ERRBIT_TIMEOUT);
-        ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -222,86 +239,83 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
     }
     umma_commit(&accum_bar);  // the accumulator is complete once every MMA has retired
-  } else if (warp >= 2) {
-    // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
+  }
+  __syncwarp();
+
+  // ---- epilogue: TMEM -> registers -> global, or -> shared memory when the cluster splits K ----
+  float* partial = reinterpret_cast<float*>(tiles);  // [tokens_pad][128 rows]; the stages are idle by then
+  if (warp >= 2) {
     wait_for_predecessor();
     const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     const int row = quarter * 32 + lane;
     const int n = n0 + row;
-    bool ok = true;
-    if (num_kb > 0) {
-      ok = mbar_wait(&accum_bar, 0);
-      if (!ok && lane == 0) atomicOr(p.err, ERRBIT_TIMEOUT);
+    bool have = num_kb > 0;
+    if (have && !mbar_wait(&accum_bar, 0)) {
+      if (lane == 0) atomicOr(p.err, ERRBIT_TIMEOUT);
+      have = false;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int tile = kBlockRows * p.tokens_pad;
-    float* column = p.scratch ? p.scratch + static_cast<int64_t>(blockIdx.x) * gridDim.y * tile : nullptr;
-    // Pass 1 (only when K is split): park this block's partial tile, laid out [token][row].
-    if (gridDim.y > 1) {
-      for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
-        float v[16];
-        if (ok && num_kb > 0) {
-          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        } else {
+    for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
+      float v[16];
+      if (have) {
+        tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+      } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+      }
+      if (members > 1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) partial[(c0 + i) * kBlockRows + row] = v[i];
+      } else if (p.epilogue == EPI_SWIGLU) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float up = __shfl_down_sync(0xffffffffu, v[i], 1);
+          const int m = c0 + i;
+          if ((lane & 1) == 0 && m < p.M && n < p.N)
+            static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
+                __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
         }
+      } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          column[static_cast<int64_t>(blockIdx.y) * tile + (c0 + i) * kBlockRows + row] = v[i];
+          if (c0 + i < p.M && n < p.N) write_output(p, c0 + i, n, v[i]);
       }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-      if (warp == 2 && lane == 0) ticket_shared = atomicAdd(&p.counters[blockIdx.x], 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      const bool last = ticket_shared == static_cast<int>(gridDim.y) - 1;
-      if (last) {
-        __threadfence();
-        if (warp == 2 && lane == 0) p.counters[blockIdx.x] = 0;  // ready for the next launch
+    }
+  }
+  if (members > 1) {
+    // Every thread of every member meets here; then each member finishes its slice of the rows.
+    cluster_sync_all();
+    int slice = (kBlockRows + members - 1) / members;
+    slice += slice & 1;  // gate/up pairs stay together
+    const int r_begin = blockIdx.y * slice, r_end = min(kBlockRows, r_begin + slice);
+    if (warp >= 2) {
+      const int tid = threadIdx.x - 64;
+      const int rows = max(0, r_end - r_begin);
+      if (p.epilogue == EPI_SWIGLU) {
+        const int pairs = rows / 2;
+        for (int item = tid; item < pairs * p.M; item += 128) {
+          const int m = item / pairs, j = item - m * pairs;
+          const int r = r_begin + 2 * j;
+          float gate = 0.f, up = 0.f;
+          for (int rank = 0; rank < members; ++rank) {
+            gate += load_peer_f32(partial + m * kBlockRows + r, rank);
+            up += load_peer_f32(partial + m * kBlockRows + r + 1, rank);
+          }
+          const int n = n0 + r;
+          if (n < p.N)
+            static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
+                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+        }
       } else {
-        ok = false;  // somebody else finishes this column
-      }
-    }
-    if (ok || (gridDim.y > 1 && ticket_shared == static_cast<int>(gridDim.y) - 1)) {
-      for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
-        float v[16];
-        if (gridDim.y > 1) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float sum = 0.f;
-            for (int s = 0; s < static_cast<int>(gridDim.y); ++s)
-              sum += __ldcg(column + static_cast<int64_t>(s) * tile + (c0 + i) * kBlockRows + row);
-            v[i] = sum;
-          }
-        } else if (num_kb > 0) {
-          tmem_load_16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = 0.f;
-        }
-        if (p.epilogue == EPI_SWIGLU) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float up = __shfl_down_sync(0xffffffffu, v[i], 1);
-            const int m = c0 + i;
-            if ((lane & 1) == 0 && m < p.M && n < p.N) {
-              const float gate = v[i];
-              static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
-                  __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = c0 + i;
-            if (m < p.M && n < p.N) {
-              if (p.epilogue == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v[i];
-              else static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(v[i]);
-            }
-          }
+        for (int item = tid; item < rows * p.M; item += 128) {
+          const int m = item / rows, r = r_begin + (item - m * rows);
+          float sum = 0.f;
+          for (int rank = 0; rank < members; ++rank) sum += load_peer_f32(partial + m * kBlockRows + r, rank);
+          if (n0 + r < p.N) write_output(p, m, n0 + r, sum);
         }
       }
     }
+    cluster_sync_all();  // nobody leaves while its shared memory is still being read
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -346,17 +360,34 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
 
 struct StreamPlan {
   int blocks;
-  int column_blocks;
+  int members;  // blocks per cluster: they share rows of W and split K
+  int stages;
+  size_t smem;
 };
 
-// A function of N and K only (see gemm_skinny.cu): about one block per SM.
-StreamPlan plan_stream(int N, int K) {
+// A function of N, K and the padded token count only (see gemm_skinny.cu for why not of M):
+// about one block per SM, and as many stages as the shared memory of the blocks that share an
+// SM allows.
+StreamPlan plan_stream(int N, int K, int tokens_pad) {
   StreamPlan plan;
   plan.blocks = (N + kBlockRows - 1) / kBlockRows;
   const int k_blocks = (K + kBlockK - 1) / kBlockK;
-  int column = max(1, min(16, 148 / plan.blocks));
-  while (column > 1 && k_blocks / column < 3) --column;  // every block keeps a few stages to stream
-  plan.column_blocks = column;
+  int members = max(1, min(8, 148 / plan.blocks));
+  while (members > 1 && k_blocks / members < 3) --members;  // every block keeps a few stages to stream
+  plan.members = members;
+  const size_t x_stride = (static_cast<size_t>(tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
+  const size_t stage = static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride;
+  const int total = plan.blocks * members;
+  const size_t budget = total <= 148 ? 200 * 1024 : (total <= 296 ? 100 * 1024 : 66 * 1024);
+  const int per_block = (k_blocks + members - 1) / members;
+  int stages = static_cast<int>(budget / stage);
+  if (const char* forced = getenv("B200_STREAM_STAGES")) stages = atoi(forced);
+  stages = stages > kMaxStages ? kMaxStages : stages;
+  stages = stages > per_block ? per_block : stages;
+  plan.stages = stages < 2 ? 2 : stages;
+  const size_t partial = static_cast<size_t>(tokens_pad) * kBlockRows * sizeof(float);
+  const size_t ring = plan.stages * stage;
+  plan.smem = (ring > partial ? ring : partial) + 1024;
   return plan;
 }
 
@@ -372,11 +403,11 @@ B200_API int b200_stream_gemm_supported(int M, int N, int K, int epilogue) {
   return 1;
 }
 
+// Kept for symmetry with the other product: this kernel needs no global scratch.
 B200_API void b200_stream_gemm_scratch(int M, int N, int K, int64_t* floats, int* counters) {
-  const StreamPlan plan = plan_stream(N, K);
-  const int tokens_pad = (M + 15) / 16 * 16;
-  *floats = plan.column_blocks > 1 ? static_cast<int64_t>(plan.blocks) * plan.column_blocks * kBlockRows * tokens_pad : 0;
-  *counters = plan.column_blocks > 1 ? plan.blocks : 0;
+  (void)M; (void)N; (void)K;
+  *floats = 0;
+  *counters = 0;
 }
 
 B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
@@ -386,17 +417,9 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
                "stream_gemm: operands must be 16-byte aligned");
-  const StreamPlan plan = plan_stream(N, K);
-  int64_t need_floats;
-  int need_counters;
-  b200_stream_gemm_scratch(M, N, K, &need_floats, &need_counters);
-  B200_REQUIRE(scratch_floats >= need_floats && num_counters >= need_counters,
-               "stream_gemm: scratch too small (%lld floats, %d counters needed)",
-               static_cast<long long>(need_floats), need_counters);
+  (void)scratch; (void)scratch_floats; (void)counters; (void)num_counters;
   StreamParams p;
   p.y = Y;
-  p.scratch = need_floats ? scratch : nullptr;
-  p.counters = counters;
   p.err = err;
   p.M = M;
   p.N = N;
@@ -405,20 +428,40 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   p.tmem_cols = 32;
   while (p.tmem_cols < p.tokens_pad) p.tmem_cols *= 2;
   p.epilogue = epilogue;
+  const StreamPlan plan = plan_stream(N, K, p.tokens_pad);
+  p.stages = plan.stages;
   CUtensorMap w_map, x_map;
   if (make_map(&w_map, W, N, K, kBlockRows) != 0) return -1;
   if (make_map(&x_map, X, M, K, p.tokens_pad) != 0) return -1;
-  const size_t x_stride = (static_cast<size_t>(p.tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
-  const size_t smem = kStagesT * (static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride) + 1024;
   static size_t configured = 0;
-  if (smem > configured) {
-    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-        cudaSuccess)
-      return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", smem);
-    configured = smem;
+  if (plan.smem > configured) {
+    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(plan.smem)) != cudaSuccess)
+      return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", plan.smem);
+    configured = plan.smem;
   }
-  const dim3 grid(plan.blocks, plan.column_blocks);
-  const cudaError_t status = launch_kernel(stream_gemm_kernel, grid, dim3(kThreadsT), smem, stream, w_map, x_map, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(plan.blocks, plan.members);
+  config.blockDim = dim3(kThreadsT);
+  config.dynamicSmemBytes = plan.smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  int count = 0;
+  if (plan.members > 1) {
+    attributes[count].id = cudaLaunchAttributeClusterDimension;
+    attributes[count].val.clusterDim.x = 1;
+    attributes[count].val.clusterDim.y = plan.members;
+    attributes[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (b200_overlap_enabled()) {
+    attributes[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  config.attrs = attributes;
+  config.numAttrs = count;
+  const cudaError_t status = cudaLaunchKernelEx(&config, stream_gemm_kernel, w_map, x_map, p);
   if (status != cudaSuccess) return b200_fail("stream_gemm: %s", cudaGetErrorString(status));
   return 0;
 }
