@@ -5,16 +5,19 @@
 // request's keys and values serves all `q_heads / kv_heads` heads that share them
 // (the reference's Metal kernel shares each K/V row the same way,
 // python/instinct/backends/metal_kernels.py:9-17,18-101). Keys and values are read straight
-// from the arena's pages through the block table, 64 keys at a time, into swizzled shared
-// memory with cp.async (double buffered); scores and the weighted sum use mma.sync
+// from the arena's pages through the block table, 64 keys at a time, into a ring of swizzled
+// shared-memory tiles with cp.async (two tiles deep; three blocks share an SM and cover each
+// other's waits); scores and the weighted sum use mma.sync
 // m16n8k16 with 32-bit accumulators and a 32-bit running softmax (max and sum per row).
 //
 // Two shapes of block, one body:
 //   * prefill: 4 warps own 16 query rows each (64 rows per block) and walk all keys;
 //   * decode : the request has one new token, its <= 16 rows are shared by the 4 warps, each
 //     warp takes a quarter of every 64-key tile, and the key range is cut into `splits`
-//     blocks whose partial results (max, sum, unnormalised output) a second kernel merges,
-//     as python/instinct/backends/metal_kernels.py:103-124 does.
+//     blocks whose partial results (max, sum, unnormalised output) a second small kernel
+//     merges, as python/instinct/backends/metal_kernels.py:103-124 does. A decode block
+//     starts fetching keys that earlier steps wrote before it waits for the kernel in front
+//     of it on the stream, which only produces the newest key.
 // Masking follows python/instinct/batches.py:110-113: key <= query position, and with a
 // window key > position - window.
 #include "common.cuh"
@@ -130,12 +133,15 @@ paged_flash_attention_kernel(const FlashParams p) {
   constexpr int kTileBytes = kTileKeys * HEAD_DIM * 2;
   // Sub-blocks of 16 keys a warp handles per 64-key tile.
   constexpr int kSubBlocks = DECODE ? 1 : kTileKeys / 16;
+  constexpr int kRing = 2;  // tiles in flight; small, so that three blocks share an SM and hide each other's waits
 
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* k_tiles = smem;                   // 2 stages
-  unsigned char* v_tiles = smem + 2 * kTileBytes;  // 2 stages
+  unsigned char* k_tiles = smem;
+  unsigned char* v_tiles = smem + kRing * kTileBytes;
 
-  wait_for_predecessor();
+  // The step's metadata (lengths, block tables) was copied to the device before any kernel of
+  // the step ran, so it may be read before the wait; queries and the newest keys may not.
+  if (!DECODE) wait_for_predecessor();
   let_successor_start();
   const int seq = p.first_seq + blockIdx.z;
   const int kv_head = blockIdx.y;
@@ -185,6 +191,33 @@ paged_flash_attention_kernel(const FlashParams p) {
   const bool live0 = r0 < rows_total, live1 = r1 < rows_total;
   const int pos0 = first_pos + tok0, pos1 = first_pos + tok1;
 
+  float o[kDimTiles][4];
+#pragma unroll
+  for (int i = 0; i < kDimTiles; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  // Fill the ring. Tiles that hold only keys of earlier steps are requested before the wait
+  // for the kernel in front (decode only); they always come first in the block's range. Every
+  // slot of the ring gets its own commit group, empty if the range is shorter.
+  auto fetch = [&](int it) {
+    const int slot = it % kRing;
+    load_tile<HEAD_DIM>(k_tiles + slot * kTileBytes, p.k_arena, table, p, kv_head, (tile_begin + it) * kTileKeys, lo, hi);
+    load_tile<HEAD_DIM>(v_tiles + slot * kTileBytes, p.v_arena, table, p, kv_head, (tile_begin + it) * kTileKeys, lo, hi);
+  };
+  int issued = 0;
+  if (DECODE) {
+    while (issued < kRing && issued < num_tiles && (tile_begin + issued + 1) * kTileKeys <= first_pos) {
+      fetch(issued);
+      cp_async_commit();
+      ++issued;
+    }
+    wait_for_predecessor();
+  }
+  for (; issued < kRing; ++issued) {
+    if (issued < num_tiles) fetch(issued);
+    cp_async_commit();
+  }
+
   // Query fragments, straight from global memory.
   uint32_t qf[kKSteps][4];
   {
@@ -200,28 +233,12 @@ paged_flash_attention_kernel(const FlashParams p) {
     }
   }
 
-  float o[kDimTiles][4];
-#pragma unroll
-  for (int i = 0; i < kDimTiles; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-
-  if (num_tiles > 0) {
-    load_tile<HEAD_DIM>(k_tiles, p.k_arena, table, p, kv_head, tile_begin * kTileKeys, lo, hi);
-    load_tile<HEAD_DIM>(v_tiles, p.v_arena, table, p, kv_head, tile_begin * kTileKeys, lo, hi);
-  }
-  cp_async_commit();
 
   for (int it = 0; it < num_tiles; ++it) {
-    const int stage = it & 1;
+    const int stage = it % kRing;
     const int tile_start = (tile_begin + it) * kTileKeys;
-    if (it + 1 < num_tiles) {
-      load_tile<HEAD_DIM>(k_tiles + (stage ^ 1) * kTileBytes, p.k_arena, table, p, kv_head,
-                          tile_start + kTileKeys, lo, hi);
-      load_tile<HEAD_DIM>(v_tiles + (stage ^ 1) * kTileBytes, p.v_arena, table, p, kv_head,
-                          tile_start + kTileKeys, lo, hi);
-    }
-    cp_async_commit();
-    cp_async_wait<1>();
+    // One group is committed per iteration, so all but the newest kRing - 1 have landed.
+    cp_async_wait<kRing - 1>();
     __syncthreads();
 
     const uint32_t k_base = smem_u32(k_tiles + stage * kTileBytes);
@@ -314,6 +331,9 @@ paged_flash_attention_kernel(const FlashParams p) {
       }
     }
     __syncthreads();
+    // The slot is free again: refill it with the tile kRing further on.
+    if (it + kRing < num_tiles) fetch(it + kRing);
+    cp_async_commit();
   }
   cp_async_wait<0>();
 
@@ -388,7 +408,8 @@ paged_flash_attention_kernel(const FlashParams p) {
   }
 }
 
-// out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M)
+// out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M), one block
+// per (token, query head) row (python/instinct/backends/metal_kernels.py:103-124).
 template <int HEAD_DIM>
 __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
                                    const float* __restrict__ partial_ml,
@@ -396,23 +417,27 @@ __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
   wait_for_predecessor();
   let_successor_start();
   const int64_t row = blockIdx.x;
-  const float* ml = partial_ml + row * splits * 2;
+  const float2* ml = reinterpret_cast<const float2*>(partial_ml + row * splits * 2);
   float m = -INFINITY;
-  for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i * 2]);
+#pragma unroll 8
+  for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i].x);
   const float use = m == -INFINITY ? 0.f : m;
   float l = 0.f;
-  for (int i = 0; i < splits; ++i) l += ml[i * 2 + 1] * exp2f(ml[i * 2] - use);
+#pragma unroll 8
+  for (int i = 0; i < splits; ++i) l += ml[i].y * exp2f(ml[i].x - use);
   const float inv = l > 0.f ? 1.f / l : 0.f;
   for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 8
     for (int i = 0; i < splits; ++i)
-      acc += partial_out[(row * splits + i) * HEAD_DIM + d] * exp2f(ml[i * 2] - use);
+      acc += partial_out[(row * splits + i) * HEAD_DIM + d] * exp2f(ml[i].x - use);
     out[row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
 template <int HEAD_DIM>
-constexpr size_t flash_smem_bytes() {
+constexpr size_t flash_smem_bytes(bool decode) {
+  (void)decode;
   const size_t tiles = 4 * static_cast<size_t>(kTileKeys) * HEAD_DIM * 2;
   const size_t merge = static_cast<size_t>(kWarps) * 16 * (HEAD_DIM + 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
@@ -421,13 +446,15 @@ constexpr size_t flash_smem_bytes() {
 template <int HEAD_DIM>
 int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, int tokens,
                  cudaStream_t stream) {
-  const size_t smem = flash_smem_bytes<HEAD_DIM>();
+  const size_t smem = flash_smem_bytes<HEAD_DIM>(decode != 0);
   static bool configured = false;
   if (!configured) {
     cudaError_t a = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(flash_smem_bytes<HEAD_DIM>(true)));
     cudaError_t b = cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(flash_smem_bytes<HEAD_DIM>(false)));
     if (a != cudaSuccess || b != cudaSuccess) return b200_fail("flash attention: cannot size shared memory");
     configured = true;
   }

@@ -47,6 +47,10 @@ B200_API int b200_embedding_gather(const void* table, int table_dtype, const int
 // kernel norms only x[rows[i]] into out[i] and leaves x alone (the model's last norm, which
 // only the wanted positions need). Formula: python/instinct/backends/portable.py:144-149;
 // the fused add follows cuda/kernels.cu:85-98 but keeps the sum in 32-bit.
+// Each thread keeps its share of the row (up to kNormCache values) in registers between the sum
+// of squares and the scaling, so the row is read from memory once; wider rows re-read.
+constexpr int kNormCache = 8;
+
 template <typename T>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
                                const float* __restrict__ weight, T* __restrict__ out,
@@ -58,21 +62,44 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
   float* xr = x + static_cast<int64_t>(r) * hidden;
   const T* dr = delta ? delta + static_cast<int64_t>(r) * hidden : nullptr;
   T* outr = out + static_cast<int64_t>(blockIdx.x) * hidden;
+  const bool cached = hidden <= kNormCache * static_cast<int>(blockDim.x);
+  float v[kNormCache];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (dr) {
-      v += to_f32<T>(dr[i]);
-      if (!rows) xr[i] = v;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < kNormCache; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      v[j] = 0.f;
+      if (i < hidden) {
+        v[j] = xr[i] + (dr ? to_f32<T>(dr[i]) : 0.f);
+        if (dr && !rows) xr[i] = v[j];
+        ss += v[j] * v[j];
+      }
     }
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float value = xr[i];
+      if (dr) {
+        value += to_f32<T>(dr[i]);
+        if (!rows) xr[i] = value;
+      }
+      ss += value * value;
+    }
   }
   const float total = block_sum(ss, scratch);
   const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (dr && rows) v += to_f32<T>(dr[i]);
-    outr[i] = from_f32<T>(v * inv * weight[i]);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < kNormCache; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) outr[i] = from_f32<T>(v[j] * inv * weight[i]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float value = xr[i];
+      if (dr && rows) value += to_f32<T>(dr[i]);
+      outr[i] = from_f32<T>(value * inv * weight[i]);
+    }
   }
 }
 
@@ -81,7 +108,7 @@ B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void
                           cudaStream_t stream) {
   if (num_rows == 0) return 0;
   B200_REQUIRE(num_rows > 0 && hidden > 0, "rmsnorm: bad sizes");
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const int threads = hidden >= 4096 ? 1024 : (hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128));
   if (dtype == DTYPE_F32) {
     launch_kernel(rmsnorm_kernel<float>, dim3(num_rows), dim3(threads), 0, stream, x,
                   static_cast<const float*>(delta), weight, static_cast<float*>(out), rows, hidden, eps);

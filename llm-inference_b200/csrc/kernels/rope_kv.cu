@@ -8,6 +8,9 @@
 // (python/instinct/paged_kv.py:259-265).
 #include "common.cuh"
 
+// One block per (token, head): query heads first, then key heads, then value heads. Thread i
+// handles pair slot i of its head (see below), so a decode step spreads over
+// tokens * (q_heads + 2 * kv_heads) small blocks instead of one block per token.
 template <typename T>
 __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
                                      const float* __restrict__ inv_freq,
@@ -18,46 +21,42 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
                                      int kv_heads, int head_dim, int rot, int page_size,
                                      int write_kv, int* __restrict__ err) {
-  extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
   wait_for_predecessor();
   let_successor_start();
   const int t = blockIdx.x;
+  const int head = blockIdx.y;  // 0 .. q_heads + 2 * kv_heads
+  const int rotated_heads = q_heads + kv_heads;
+  const bool is_q = head < q_heads, is_k = !is_q && head < rotated_heads;
+  if (!is_q && !write_kv) return;
   const int pos = positions[t];
-  const int half_rot = rot / 2;
-  for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
-    float s, c;
-    sincosf(static_cast<float>(pos) * inv_freq[i], &s, &c);
-    trig[i] = c;
-    trig[half_rot + i] = s;
-  }
-  __syncthreads();
+  const int half_rot = rot / 2, half = head_dim / 2;
 
-  int page = -1;
-  if (write_kv) {
+  T* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<int64_t>(t) * q_heads + head) * head_dim;
+  } else {
     const int logical = pos / page_size;
     if (pos < 0 || logical >= max_pages) {
       if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_POSITION);
-    } else {
-      page = block_table[static_cast<int64_t>(token_seq[t]) * max_pages + logical];
-      if (page < 0 || page >= num_pages) {
-        if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
-        page = -1;
-      }
+      return;
     }
+    const int page = block_table[static_cast<int64_t>(token_seq[t]) * max_pages + logical];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
+      return;
+    }
+    const int kv_head = is_k ? head - q_heads : head - rotated_heads;
+    dst = (is_k ? k_arena : v_arena) + kv_row_offset(page, kv_head, pos % page_size, kv_heads, page_size, head_dim);
   }
-  const int row = pos % page_size;
   const int width = (q_heads + 2 * kv_heads) * head_dim;
-  const T* src = qkv + static_cast<int64_t>(t) * width;
-  const int half = head_dim / 2;
-  const int rotated_heads = q_heads + kv_heads;
+  const T* src = qkv + static_cast<int64_t>(t) * width + head * head_dim;
+  const float* b = bias ? bias + head * head_dim : nullptr;
 
-  // One work item per (head, pair slot): slots below rot/2 are rotated pairs, the rest copy
-  // the two trailing dims that a partial rotation leaves alone.
-  for (int item = threadIdx.x; item < rotated_heads * half; item += blockDim.x) {
-    const int head = item / half;
-    const int slot = item - head * half;
+  // Pair slot i: below rot/2 it is the rotated pair (i, i + rot/2); the rest are the two
+  // trailing dims a partial rotation leaves alone. Value heads are copied (bias added).
+  for (int slot = threadIdx.x; slot < half; slot += blockDim.x) {
     int d0, d1;
-    float y0, y1;
+    const bool rotate = (is_q || is_k) && slot < half_rot;
     if (slot < half_rot) {
       d0 = slot;
       d1 = slot + half_rot;
@@ -65,39 +64,20 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
       d0 = rot + 2 * (slot - half_rot);
       d1 = d0 + 1;
     }
-    float x0 = to_f32<T>(src[head * head_dim + d0]);
-    float x1 = to_f32<T>(src[head * head_dim + d1]);
-    if (bias) {
-      x0 += bias[head * head_dim + d0];
-      x1 += bias[head * head_dim + d1];
+    float x0 = to_f32<T>(src[d0]), x1 = to_f32<T>(src[d1]);
+    if (b) {
+      x0 += b[d0];
+      x1 += b[d1];
     }
-    if (slot < half_rot) {
-      const float c = trig[slot], s = trig[half_rot + slot];
-      y0 = x0 * c - x1 * s;
-      y1 = x1 * c + x0 * s;
-    } else {
-      y0 = x0;
-      y1 = x1;
+    if (rotate) {
+      float sn, cs;
+      sincosf(static_cast<float>(pos) * inv_freq[slot], &sn, &cs);
+      const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
+      x0 = y0;
+      x1 = y1;
     }
-    if (head < q_heads) {
-      T* dst = q_out + (static_cast<int64_t>(t) * q_heads + head) * head_dim;
-      dst[d0] = from_f32<T>(y0);
-      dst[d1] = from_f32<T>(y1);
-    } else if (page >= 0) {
-      T* dst = k_arena + kv_row_offset(page, head - q_heads, row, kv_heads, page_size, head_dim);
-      dst[d0] = from_f32<T>(y0);
-      dst[d1] = from_f32<T>(y1);
-    }
-  }
-  if (page >= 0) {
-    const int v_base = rotated_heads * head_dim;
-    for (int item = threadIdx.x; item < kv_heads * head_dim; item += blockDim.x) {
-      const int head = item / head_dim;
-      const int d = item - head * head_dim;
-      float x = to_f32<T>(src[v_base + item]);
-      if (bias) x += bias[v_base + item];
-      v_arena[kv_row_offset(page, head, row, kv_heads, page_size, head_dim) + d] = from_f32<T>(x);
-    }
+    dst[d0] = from_f32<T>(x0);
+    dst[d1] = from_f32<T>(x1);
   }
 }
 
@@ -114,15 +94,17 @@ B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float*
   B200_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0,
                "rope_kv_write: rotary dims %d must be even and at most head_dim %d", rot, head_dim);
   B200_REQUIRE(page_size > 0 && max_pages > 0, "rope_kv_write: bad page geometry");
-  const int threads = 128;
-  const size_t smem = sizeof(float) * (rot > 0 ? rot : 2);
+  const int threads = head_dim >= 128 ? 64 : 32;
+  const size_t smem = 0;
+  const dim3 grid(tokens, q_heads + 2 * kv_heads);
+  B200_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
   if (dtype == DTYPE_F32) {
-    launch_kernel(rope_kv_write_kernel<float>, dim3(tokens), dim3(threads), smem, stream,
+    launch_kernel(rope_kv_write_kernel<float>, grid, dim3(threads), smem, stream,
         static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, block_table,
         max_pages, num_pages, static_cast<float*>(k_arena), static_cast<float*>(v_arena),
         static_cast<float*>(q_out), q_heads, kv_heads, head_dim, rot, page_size, write_kv, err);
   } else if (dtype == DTYPE_BF16) {
-    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream,
+    launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream,
         static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, block_table,
         max_pages, num_pages, static_cast<__nv_bfloat16*>(k_arena),
         static_cast<__nv_bfloat16*>(v_arena), static_cast<__nv_bfloat16*>(q_out), q_heads,

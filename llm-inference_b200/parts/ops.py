@@ -88,10 +88,23 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
     choice = ctx.options.get("gemm", "auto")
     if choice == "library":
         return None
-    if choice in ("auto", "tcgen05") and ctx.lib.lib.b200_stream_gemm_supported(m, n, k, epilogue):
+    stream = bool(ctx.lib.lib.b200_stream_gemm_supported(m, n, k, epilogue))
+    skinny = bool(ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue))
+    if choice == "tcgen05":
+        return "stream" if stream else None
+    if choice == "skinny":
+        return "skinny" if skinny else None
+    # auto, from measurements on a B200 (graph-timed, weights from HBM): for up to 16 rows the
+    # mma.sync kernel wins on small matrices, whose time is all launch and ramp, and the
+    # tcgen05 kernel on large ones (long K or very many rows of W); with more rows of X the
+    # vendor library's tiles serve the mid-sized matrices better.
+    weight_bytes = 2 * n * k
+    if m <= 16:
+        if skinny and weight_bytes < (16 << 20):
+            return "skinny"
+        return "stream" if stream else ("skinny" if skinny else None)
+    if stream and (weight_bytes >= (256 << 20) or (n <= 2048 and k >= 4096)):
         return "stream"
-    if choice in ("auto", "skinny") and ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue):
-        return "skinny"
     return None
 
 
@@ -252,10 +265,13 @@ def flash_attention_supported(ctx: StepContext, q_heads: int, kv_heads: int, hea
 
 
 def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int) -> int:
-    """How many blocks cut each request's keys so that a decode step fills the GPU."""
+    """How many blocks cut each request's keys in a decode step: about two waves of blocks
+    (three blocks fit an SM), at least one 64-key tile each, and few enough that the merge
+    of their partial results stays cheap."""
     tiles = max(1, (max_kv_len + 63) // 64)
-    want = -(-2 * NUM_SMS // max(1, num_seqs * kv_heads))
-    return max(1, min(want, tiles))
+    pairs = max(1, num_seqs * kv_heads)
+    want = -(-6 * NUM_SMS // pairs)
+    return max(1, min(tiles, 16, want))
 
 
 def paged_flash_attention(
