@@ -133,8 +133,9 @@ class ClockSampler:
 
 def reference_arm() -> int:
     reason = (
-        "the reference's tested engine needs MLX (Apple/Metal; not installable offline here) and its "
-        "CUDA engine does not compile with CUDA 12.9 (nvToolsExt.h is gone) and has never run on a GPU"
+        "the reference does not install offline here: pip finds no numpy wheel for its dependency, and with "
+        "--no-deps its CMake build fails (CUDA::nvToolsExt is not in CUDA 12.9); its only engine that has "
+        "ever run needs MLX on Apple hardware"
     )
     print(json.dumps({"impl": "reference", "unavailable": reason}))
     return 0
