@@ -295,3 +295,83 @@ B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int 
   if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
   return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
 }
+
+// ---- the variant that allocates nothing (declared and documented in gemm_skinny_static.h) ----
+#include <mutex>
+
+#include "gemm_skinny_static.h"
+
+namespace {
+
+constexpr long long kStaticScratchFloats = 128 * 1024;  // 512 KiB of partial sums
+constexpr int kStaticCounters = 1024;
+constexpr int kMaxDevices = 64;
+
+// In host code these names are stand-ins for the device arrays, not device addresses: the
+// addresses come from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+static __device__ __align__(256) int g_static_counters[kStaticCounters];
+
+struct StaticScratch {
+  float* scratch = nullptr;
+  int* counters = nullptr;
+};
+StaticScratch g_static_by_device[kMaxDevices];
+std::mutex g_static_mutex;
+
+// The device addresses of the arrays on the current device, looked up once per device.
+int static_scratch(StaticScratch* out) {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices)
+    return b200_fail("skinny_gemm_static: cannot tell the current device");
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratch& entry = g_static_by_device[device];
+  if (entry.scratch == nullptr) {
+    float* scratch = nullptr;
+    int* counters = nullptr;
+    cudaError_t status = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_static_scratch);
+    if (status != cudaSuccess)
+      return b200_fail("skinny_gemm_static: cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(status));
+    status = cudaGetSymbolAddress(reinterpret_cast<void**>(&counters), g_static_counters);
+    if (status != cudaSuccess)
+      return b200_fail("skinny_gemm_static: cudaGetSymbolAddress(counters) failed: %s", cudaGetErrorString(status));
+    entry.scratch = scratch;
+    entry.counters = counters;
+  }
+  *out = entry;
+  return 0;
+}
+
+}  // namespace
+
+B200_API long long b200_skinny_gemm_static_capacity_floats(void) { return kStaticScratchFloats; }
+
+B200_API int b200_skinny_gemm_static(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
+                                     cudaStream_t stream) {
+  B200_REQUIRE(b200_skinny_gemm_supported(M, N, K, epilogue),
+               "skinny_gemm_static: unsupported shape %d x %d x %d (at most 16 rows, K a multiple of 8)", M, N, K);
+  B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "skinny_gemm_static: unknown epilogue %d", epilogue);
+  B200_REQUIRE(W != nullptr && X != nullptr && Y != nullptr, "skinny_gemm_static: null operand");
+  B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
+               "skinny_gemm_static: operands must be 16-byte aligned");
+  int64_t need_floats = 0;
+  int need_counters = 0;
+  b200_skinny_gemm_scratch(M, N, K, &need_floats, &need_counters);
+  B200_REQUIRE(need_floats <= kStaticScratchFloats && need_counters <= kStaticCounters,
+               "skinny_gemm_static: %d x %d x %d needs %lld floats and %d counters of scratch; the static scratch "
+               "holds %lld floats and %d counters",
+               M, N, K, static_cast<long long>(need_floats), need_counters, kStaticScratchFloats, kStaticCounters);
+  StaticScratch mine;
+  if (static_scratch(&mine) != 0) return -1;
+  if (need_counters > 0) {
+    // The counters are the only part that must start at zero.
+    const cudaError_t status = cudaMemsetAsync(mine.counters, 0, sizeof(int) * need_counters, stream);
+    if (status != cudaSuccess)
+      return b200_fail("skinny_gemm_static: clearing the counters failed: %s", cudaGetErrorString(status));
+  }
+  const SkinnyPlan plan = plan_skinny(N, K);
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
+  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream);
+}
