@@ -1,0 +1,54 @@
+"""Command-line entry points."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+from helpers import ROOT, plain_weights
+from plain import qwen2_plain as plain
+
+
+def run(module: str, *args: str, check: bool = True) -> subprocess.CompletedProcess:
+    result = subprocess.run(
+        [sys.executable, "-m", f"llm_inference_b200.cli.{module}", *args], capture_output=True, text=True, cwd=ROOT, timeout=600
+    )
+    if check:
+        assert result.returncode == 0, result.stderr[-3000:]
+    return result
+
+
+def test_random_model_and_inspect(tmp_path):
+    folder = tmp_path / "tiny"
+    run("random_model", "--preset", "tiny-b", "--seed", "4", "--out", str(folder))
+    assert json.loads((folder / "config.json").read_text())["sliding_window"] == 24
+    out = run("inspect_model", str(folder)).stdout
+    assert "architecture: Qwen2ForCausalLM" in out and "lm_head.weight  bfloat16  [311, 96]" in out and "valid" in out
+    (folder / "config.json").write_text(json.dumps({"architectures": ["Nope"]}))
+    bad = run("inspect_model", str(folder), check=False)
+    assert bad.returncode == 1 and "no model registered for 'Nope'" in bad.stderr
+
+
+@pytest.mark.gpu
+def test_generate_and_benchmark(tmp_path):
+    folder = tmp_path / "tiny"
+    run("random_model", "--preset", "tiny-a", "--seed", "9", "--out", str(folder))
+    config, weights = plain_weights(folder)
+    prompt = [5, 17, 3, 200, 41]
+    out = run("generate", "--model", str(folder), "--prompt-ids", "5,17,3,200,41", "--max-new-tokens", "6",
+              "--dtype", "float32", "--max-model-length", "128", "--kv-cache-mib", "1", "--page-size", "16").stdout
+    assert json.loads(out.strip().splitlines()[-1])["tokens"] == plain.greedy(config, weights, prompt, 6)
+    prompts = tmp_path / "prompts.json"
+    prompts.write_text(json.dumps([[1, 2, 3], list(range(40)), [9] * 17]))
+    result = tmp_path / "bench.json"
+    run("benchmark", "--model", str(folder), "--prompts", str(prompts), "--output", str(result), "--output-length", "8",
+        "--warmups", "1", "--repetitions", "2", "--max-sequences", "2", "--max-model-length", "128", "--kv-cache-mib", "1",
+        "--page-size", "16")
+    report = json.loads(result.read_text())
+    assert report["aggregate"]["generated_tokens_per_second"] > 0
+    assert len(report["requests"]) == 6 and all(r["output_tokens"] == 8 for r in report["requests"])
+    assert set(report["aggregate"]["ttft_ms"]) == {"p50", "p95", "p99"}
