@@ -131,8 +131,6 @@ paged_flash_attention_kernel(const FlashParams p) {
   constexpr int kKSteps = HEAD_DIM / 16;   // k-steps of the score product
   constexpr int kDimTiles = HEAD_DIM / 8;  // n-tiles of the output
   constexpr int kTileBytes = kTileKeys * HEAD_DIM * 2;
-  // Sub-blocks of 16 keys a warp handles per 64-key tile.
-  constexpr int kSubBlocks = DECODE ? 1 : kTileKeys / 16;
   constexpr int kRing = 2;  // tiles in flight; small, so that three blocks share an SM and hide each other's waits
 
   extern __shared__ __align__(128) unsigned char smem[];
@@ -248,36 +246,39 @@ paged_flash_attention_kernel(const FlashParams p) {
         (tile_start + kTileKeys - 1 > first_pos + min(tok0, q_len - 1)) ||
         (p.window > 0 && tile_start <= pos1 - p.window) || (tile_start < lo) || !live1;
 
+    {
+      // A prefill warp takes all 64 keys of the tile for its 16 rows (eight independent score
+      // tiles, one softmax update per tile); a decode warp takes its quarter of the tile.
+      constexpr int kGroups = DECODE ? 1 : kTileKeys / 16;  // groups of 16 keys per warp per tile
+      const int group0 = DECODE ? warp : 0;
+      const int key_base = tile_start + group0 * 16;
+      float s[2 * kGroups][4];
 #pragma unroll
-    for (int sb = 0; sb < kSubBlocks; ++sb) {
-      const int sub = DECODE ? warp : sb;  // which 16 keys of the tile
-      const int key0 = tile_start + sub * 16;
-      if (!DECODE && key0 > hi) break;
-      // Scores of 16 rows x 16 keys: two n-tiles of 8 keys.
-      float s[2][4];
-#pragma unroll
-      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < 2 * kGroups; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
       {
         const int mi = lane >> 3;
-        const int krow = sub * 16 + (mi >> 1) * 8 + (lane & 7);
 #pragma unroll
         for (int ks = 0; ks < kKSteps; ++ks) {
-          uint32_t b[4];
-          ldmatrix_x4(b, k_base + tile_offset<HEAD_DIM>(krow, ks * 2 + (mi & 1)));
-          mma_bf16(s[0], qf[ks], b[0], b[1]);
-          mma_bf16(s[1], qf[ks], b[2], b[3]);
+#pragma unroll
+          for (int gidx = 0; gidx < kGroups; ++gidx) {
+            const int krow = (group0 + gidx) * 16 + (mi >> 1) * 8 + (lane & 7);
+            uint32_t b[4];
+            ldmatrix_x4(b, k_base + tile_offset<HEAD_DIM>(krow, ks * 2 + (mi & 1)));
+            mma_bf16(s[2 * gidx], qf[ks], b[0], b[1]);
+            mma_bf16(s[2 * gidx + 1], qf[ks], b[2], b[3]);
+          }
         }
       }
       // Scale, mask, running softmax. Element (n, e): row = e < 2 ? r0 : r1,
-      // key = key0 + n * 8 + (lane % 4) * 2 + (e & 1).
+      // key = key_base + n * 8 + (lane % 4) * 2 + (e & 1).
       float tile_max0 = -INFINITY, tile_max1 = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 2 * kGroups; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = s[n][e] * p.scale_log2;
           if (tile_needs_mask) {
-            const int key = key0 + n * 8 + (lane & 3) * 2 + (e & 1);
+            const int key = key_base + n * 8 + (lane & 3) * 2 + (e & 1);
             const int pos = e < 2 ? pos0 : pos1;
             const bool live = e < 2 ? live0 : live1;
             const bool visible = live && key <= pos && key >= lo && (p.window == 0 || key > pos - p.window);
@@ -298,15 +299,15 @@ paged_flash_attention_kernel(const FlashParams p) {
       m0 = new0;
       m1 = new1;
       float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pf[4];
+      uint32_t pf[kGroups][4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < 2 * kGroups; ++n) {
         const float p00 = exp2f(s[n][0] - use0), p01 = exp2f(s[n][1] - use0);
         const float p10 = exp2f(s[n][2] - use1), p11 = exp2f(s[n][3] - use1);
         sum0 += p00 + p01;
         sum1 += p10 + p11;
-        pf[n * 2 + 0] = pack_bf16(p00, p01);  // rows r0: a0/a1 (n = 0), a4/a5 (n = 1)
-        pf[n * 2 + 1] = pack_bf16(p10, p11);  // rows r1: a2/a3 (n = 0), a6/a7 (n = 1)
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p00, p01);  // rows r0: a0/a1 (even n), a4/a5 (odd n)
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p10, p11);  // rows r1: a2/a3 (even n), a6/a7 (odd n)
       }
       l0 = l0 * alpha0 + sum0;
       l1 = l1 * alpha1 + sum1;
@@ -317,16 +318,19 @@ paged_flash_attention_kernel(const FlashParams p) {
         o[i][2] *= alpha1;
         o[i][3] *= alpha1;
       }
-      // O += P V over these 16 keys.
+      // O += P V over the warp's keys, 16 at a time.
       {
         const int mi = lane >> 3;
-        const int vrow = sub * 16 + (mi & 1) * 8 + (lane & 7);
 #pragma unroll
-        for (int c = 0; c < kDimTiles; c += 2) {
-          uint32_t b[4];
-          ldmatrix_x4_trans(b, v_base + tile_offset<HEAD_DIM>(vrow, c + (mi >> 1)));
-          mma_bf16(o[c], pf, b[0], b[1]);
-          mma_bf16(o[c + 1], pf, b[2], b[3]);
+        for (int gidx = 0; gidx < kGroups; ++gidx) {
+          const int vrow = (group0 + gidx) * 16 + (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+          for (int c = 0; c < kDimTiles; c += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_base + tile_offset<HEAD_DIM>(vrow, c + (mi >> 1)));
+            mma_bf16(o[c], pf[gidx], b[0], b[1]);
+            mma_bf16(o[c + 1], pf[gidx], b[2], b[3]);
+          }
         }
       }
     }
