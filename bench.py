@@ -258,11 +258,13 @@ def main() -> int:
         replays_before = runner.graph_replays
         mark = sampler.mark()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push(f"decode_timed_b{batch}")
         start.record()
         for step in range(w, w + k):
             one(step)
         end.record()
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
         ms = start.elapsed_time(end) / k
         replays = runner.graph_replays - replays_before
         launches = (runner.lib.calls - calls_before) + replays * runner.launches_per_graph.get(runner._bucket(batch), 0)
@@ -298,7 +300,10 @@ def main() -> int:
     elapsed = time.perf_counter() - begin
     for r in request_ids:
         engine.cancel(r)
-    layout_words = 3 * args.batch + 4 * args.batch + args.batch + args.batch * cache.max_pages_per_request
+    # One pinned-to-device copy of the step's metadata (tokens, positions, lengths, block tables,
+    # padded to the captured batch size) and one device-to-host read of the sampled tokens.
+    bucket = runner._bucket(args.batch)
+    layout_words = 3 * bucket + 4 * bucket + bucket + len(cache.groups) * bucket * cache.max_pages_per_request
     e2e = {
         "value": emitted / elapsed, "unit": "tokens/s", "h2d_bytes_per_step": 4 * layout_words,
         "d2h_bytes_per_step": 4 * (args.batch + 1),
