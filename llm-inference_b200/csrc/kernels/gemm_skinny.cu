@@ -65,7 +65,8 @@ template <int MT>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                    void* __restrict__ Y, int M, int N, int K, int row_groups, int epilogue,
-                   float* __restrict__ scratch, int* __restrict__ counters) {
+                   float* __restrict__ scratch, int* __restrict__ counters, const void* __restrict__ next_weights,
+                   long long next_bytes) {
   // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* ring = reinterpret_cast<uint4*>(smem_raw);
@@ -112,6 +113,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
 #pragma unroll
   for (int i = 0; i < kStages; ++i) fetch_w(c_begin + i, i);
   copy_async_commit();
+  prefetch_slice_to_l2(next_weights, next_bytes);
   wait_for_predecessor();
   let_successor_start();
 #pragma unroll
@@ -233,7 +235,8 @@ SkinnyPlan plan_skinny(int N, int K) {
 
 template <int MT>
 int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
-                  const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream) {
+                  const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
+                  const void* next_weights = nullptr, long long next_bytes = 0) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
   const size_t ring = static_cast<size_t>(kSkinnyWarps) * kStages * (2 + MT) * 32 * 16;
@@ -248,7 +251,7 @@ int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M
   }
   const dim3 grid(plan.blocks, plan.column_blocks);
   cudaError_t status = launch_kernel(skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X, Y, M,
-                                     N, K, plan.row_groups, epilogue, scratch, counters);
+                                     N, K, plan.row_groups, epilogue, scratch, counters, next_weights, next_bytes);
   if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
   return 0;
 }
@@ -276,9 +279,11 @@ B200_API void b200_skinny_gemm_scratch(int M, int N, int K, int64_t* floats, int
   *counters = plan.column_blocks > 1 ? plan.blocks : 0;
 }
 
+// `next_weights` / `next_bytes` (may be null / 0): memory the kernel asks the L2 cache to fetch
+// while it runs, meant for the weights of the product that follows on the stream.
 B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
                               float* scratch, int64_t scratch_floats, int* counters, int num_counters,
-                              cudaStream_t stream) {
+                              const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
   B200_REQUIRE(b200_skinny_gemm_supported(M, N, K, epilogue), "skinny_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "skinny_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -292,8 +297,8 @@ B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int 
                static_cast<long long>(need_floats), need_counters);
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
-  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream);
+  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes);
 }
 
 // ---- the variant that allocates nothing (declared and documented in gemm_skinny_static.h) ----

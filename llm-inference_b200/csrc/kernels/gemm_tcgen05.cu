@@ -128,6 +128,8 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
 struct StreamParams {
   void* y;
   int* err;
+  const void* next_weights;  // fetched into L2 while this product runs (may be null)
+  long long next_bytes;
   int stages;
   int M, N, K;
   int tokens_pad;  // MMA N: M rounded up to a multiple of 16
@@ -195,6 +197,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_shared;
 
+  prefetch_slice_to_l2(p.next_weights, p.next_bytes);
   if (warp == 0 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------------
     // Weights of the first stages go out before the dependency wait; X follows it.
@@ -415,7 +418,7 @@ B200_API void b200_stream_gemm_scratch(int M, int N, int K, int64_t* floats, int
 
 B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
                               float* scratch, int64_t scratch_floats, int* counters, int num_counters, int* err,
-                              cudaStream_t stream) {
+                              const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
   B200_REQUIRE(b200_stream_gemm_supported(M, N, K, epilogue), "stream_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -424,6 +427,8 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   StreamParams p;
   p.y = Y;
   p.err = err;
+  p.next_weights = next_weights;
+  p.next_bytes = next_bytes;
   p.M = M;
   p.N = N;
   p.K = K;

@@ -57,8 +57,8 @@ _SIGNATURES: dict[str, list] = {
     + [c_float, c_int, c_void_p, c_void_p],
     "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
     "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
-    "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p],
-    "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p],
+    "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p],
+    "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p],
     "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p],
     "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p],
 }

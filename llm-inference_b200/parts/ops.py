@@ -150,6 +150,18 @@ def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Te
     ]
     if kernel == "stream":
         args.append(ptr(ctx.err))
+    # The weights of the product that follows this one in the step, if the runner has learnt the
+    # order: this kernel asks the L2 cache to fetch them while it runs.
+    trace = ctx.options.get("gemm_trace")
+    if trace is not None:
+        trace.append((weight.data_ptr(), weight.numel() * weight.element_size()))
+    upcoming = ctx.options.get("gemm_next", {}).get(weight.data_ptr())
+    if upcoming is not None:
+        from ctypes import c_void_p
+
+        args += [c_void_p(upcoming[0]), c_int64(min(upcoming[1], ctx.options.get("prefetch_bytes", 64 << 20)))]
+    else:
+        args += [ptr(None), c_int64(0)]
     ctx.lib.call(f"b200_{kernel}_gemm", *args, ctx.stream)
 
 
