@@ -47,6 +47,7 @@ struct FlashParams {
   int page_shift, page_mask;
   int window;
   int splits;
+  int cluster_merge;  // the splits of a (request, kv head) are one thread-block cluster and merge on chip
   float scale_log2;
 };
 
@@ -365,6 +366,8 @@ paged_flash_attention_kernel(const FlashParams p) {
   __syncthreads();
   float* merge_o = reinterpret_cast<float*>(smem);                  // [warps][16][HEAD_DIM]
   float* merge_ml = merge_o + kWarps * 16 * HEAD_DIM;                // [warps][16][2]
+  float* block_o = merge_ml + kWarps * 16 * 2;                       // [16][HEAD_DIM], this block's result
+  float* block_ml = block_o + 16 * HEAD_DIM;                         // [16][2]
   {
     const int lr0 = lane >> 2, lr1 = lr0 + 8;
 #pragma unroll
@@ -402,6 +405,12 @@ paged_flash_attention_kernel(const FlashParams p) {
     const int64_t out_row = static_cast<int64_t>(q_start + tok) * p.q_heads + head;
     if (p.splits == 1) {
       p.out[out_row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else if (p.cluster_merge) {
+      block_o[row * HEAD_DIM + d] = acc;
+      if (d == 0) {
+        block_ml[row * 2 + 0] = m;
+        block_ml[row * 2 + 1] = l;
+      }
     } else {
       p.partial_out[(out_row * p.splits + split) * HEAD_DIM + d] = acc;
       if (d == 0) {
@@ -410,6 +419,53 @@ paged_flash_attention_kernel(const FlashParams p) {
       }
     }
   }
+  if (p.splits == 1 || !p.cluster_merge) return;
+
+  // The splits of this (request, kv head) are the blocks of one cluster. Each left its partial
+  // result in its own shared memory; after a cluster barrier every block finishes a slice of
+  // the head dims, adding the splits in rank order through distributed shared memory:
+  // out = sum_i o_i 2^(m_i - M) / sum_i l_i 2^(m_i - M).
+  cluster_sync_all();
+  {
+    // Weights of the splits per row, gathered once: weight[r][row] = 2^(m_r - M) / L.
+    float* weight = merge_o;  // [splits][16]; the warps' partials are no longer needed
+    for (int item = threadIdx.x; item < p.splits * 16; item += kFlashThreads) {
+      const int r = item >> 4, row = item & 15;
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (row < rows_total) {
+        ml.x = load_peer_f32(block_ml + row * 2, r);
+        ml.y = load_peer_f32(block_ml + row * 2 + 1, r);
+      }
+      weight[item] = ml.x;
+      weight[p.splits * 16 + item] = ml.y;
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+      const int row = threadIdx.x;
+      float m = -INFINITY;
+      for (int r = 0; r < p.splits; ++r) m = fmaxf(m, weight[r * 16 + row]);
+      const float use = m == -INFINITY ? 0.f : m;
+      float l = 0.f;
+      for (int r = 0; r < p.splits; ++r) l += weight[p.splits * 16 + r * 16 + row] * exp2f(weight[r * 16 + row] - use);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      for (int r = 0; r < p.splits; ++r) weight[r * 16 + row] = exp2f(weight[r * 16 + row] - use) * inv;
+    }
+    __syncthreads();
+    const int slice = (HEAD_DIM + p.splits - 1) / p.splits;
+    const int d_begin = split * slice, d_end = min(HEAD_DIM, d_begin + slice);
+    const int width = max(0, d_end - d_begin);
+    for (int item = threadIdx.x; item < rows_total * width; item += kFlashThreads) {
+      const int row = item / width, d = d_begin + (item - row * width);
+      float acc = 0.f;
+#pragma unroll 8
+      for (int r = 0; r < p.splits; ++r) acc += load_peer_f32(block_o + row * HEAD_DIM + d, r) * weight[r * 16 + row];
+      const int tok = row / p.group;
+      const int head = kv_head * p.group + (row - tok * p.group);
+      const int64_t out_row = static_cast<int64_t>(q_start + tok) * p.q_heads + head;
+      p.out[out_row * HEAD_DIM + d] = __float2bfloat16_rn(acc);
+    }
+  }
+  cluster_sync_all();  // nobody leaves while its shared memory is still being read
 }
 
 // out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M), one block
@@ -443,7 +499,7 @@ template <int HEAD_DIM>
 constexpr size_t flash_smem_bytes(bool decode) {
   (void)decode;
   const size_t tiles = 4 * static_cast<size_t>(kTileKeys) * HEAD_DIM * 2;
-  const size_t merge = static_cast<size_t>(kWarps) * 16 * (HEAD_DIM + 2) * sizeof(float);
+  const size_t merge = static_cast<size_t>(kWarps + 1) * 16 * (HEAD_DIM + 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
 
@@ -464,6 +520,32 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
   }
   if (decode) {
     const dim3 grid(p.splits, p.kv_heads, num_seqs);
+    if (p.splits > 1 && p.cluster_merge) {
+      static bool wide_clusters = false;
+      if (p.splits > 8 && !wide_clusters) {
+        if (cudaFuncSetAttribute(paged_flash_attention_kernel<HEAD_DIM, true>,
+                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+          return b200_fail("flash attention: clusters of %d blocks are not allowed here", p.splits);
+        wide_clusters = true;
+      }
+      cudaLaunchConfig_t config = {};
+      config.gridDim = grid;
+      config.blockDim = dim3(kFlashThreads);
+      config.dynamicSmemBytes = smem;
+      config.stream = stream;
+      cudaLaunchAttribute attributes[2];
+      attributes[0].id = cudaLaunchAttributeClusterDimension;
+      attributes[0].val.clusterDim.x = p.splits;
+      attributes[0].val.clusterDim.y = 1;
+      attributes[0].val.clusterDim.z = 1;
+      attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attributes[1].val.programmaticStreamSerializationAllowed = 1;
+      config.attrs = attributes;
+      config.numAttrs = b200_overlap_enabled() ? 2 : 1;
+      const cudaError_t status = cudaLaunchKernelEx(&config, paged_flash_attention_kernel<HEAD_DIM, true>, p);
+      if (status != cudaSuccess) return b200_fail("flash attention: %s", cudaGetErrorString(status));
+      return 0;
+    }
     launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
       launch_kernel(flash_merge_kernel<HEAD_DIM>, dim3(tokens * p.q_heads), dim3(HEAD_DIM <= 64 ? 64 : 128), 0,
@@ -496,8 +578,10 @@ B200_API int64_t b200_flash_attention_scratch_floats(int tokens, int q_heads, in
 }
 
 // Attention for requests [first_seq, first_seq + num_seqs) of the step. With `decode` each of
-// them has exactly one new token and `tokens` = num_seqs; `scratch` holds the partial
-// results when splits > 1. Query and output rows are indexed by the step's token rows.
+// them has exactly one new token and `tokens` = num_seqs. With splits > 1 the partial results
+// are merged either on chip (scratch == nullptr, at most 16 splits: they form a thread-block
+// cluster) or through `scratch` by a second kernel. Query and output rows are indexed by the
+// step's token rows.
 B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, const void* v_arena,
                                         void* out, const int* block_table, const int* seq_q_start,
                                         const int* seq_q_len, const int* seq_kv_len, int first_seq,
@@ -511,7 +595,8 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
                kv_heads, head_dim, page_size);
   B200_REQUIRE(num_seqs > 0 && num_seqs <= 65535 && splits >= 1 && max_q_len >= 1,
                "paged_flash_attention: bad batch");
-  B200_REQUIRE(splits == 1 || (decode && scratch != nullptr), "paged_flash_attention: splits need scratch");
+  B200_REQUIRE(splits == 1 || (decode && (scratch != nullptr || splits <= 16)),
+               "paged_flash_attention: more than 16 splits need scratch");
   FlashParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_arena = static_cast<const __nv_bfloat16*>(k_arena);
@@ -533,6 +618,7 @@ B200_API int b200_paged_flash_attention(const void* q, const void* k_arena, cons
   p.page_mask = page_size - 1;
   p.window = window;
   p.splits = decode ? splits : 1;
+  p.cluster_merge = (scratch == nullptr && p.splits > 1) ? 1 : 0;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;

@@ -60,6 +60,21 @@ __device__ __forceinline__ void prefetch_slice_to_l2(const void* base, long long
   }
 }
 
+// Thread-block clusters: a barrier over every thread of every block of the cluster, and a
+// 32-bit load from the same shared-memory address in another block of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 bool b200_overlap_enabled();
 
 template <typename... KernelArgs, typename... Args>

@@ -137,17 +137,6 @@ struct StreamParams {
   int epilogue;
 };
 
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
-
 __device__ __forceinline__ void write_output(const StreamParams& p, int m, int n, float v) {
   if (p.epilogue == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v;
   else static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(v);

@@ -450,7 +450,10 @@ def test_paged_flash_attention(lib, case):
     while lead < len(runs) and runs[lead] == 1:
         lead += 1
     if lead and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, page, True):
-        for splits in (1, 3, 40):
+        # One block per request; splits merged on chip by a cluster (3, 8, 16 blocks) or through
+        # scratch memory by a second kernel (3, 40).
+        for splits, merge in ((1, "cluster"), (3, "cluster"), (8, "cluster"), (16, "cluster"), (3, "scratch"), (40, "scratch")):
+            ctx.options["attention_merge"] = merge
             out3 = torch.full_like(q, float("nan"))
             ops.paged_flash_attention(ctx, view, q, out3, q_heads, kv_heads, head_dim, head_dim**-0.5,
                                       first_seq=0, num_seqs=lead, decode=True, max_q_len=1, splits=splits)
