@@ -95,34 +95,60 @@ __device__ __forceinline__ int tile_offset(int row, int chunk) {
   return row * (HEAD_DIM * 2) + ((chunk ^ (row & 7)) << 4);
 }
 
-// Copies keys [tile_start, tile_start + 64) of one kv head into a shared-memory tile; rows
-// outside [lo, hi] are zero-filled (they may lie in pages the request no longer holds).
+// Copies keys and values [tile_start, tile_start + 64) of one kv head into their shared-memory
+// tiles; rows outside [lo, hi] are zero-filled (they may lie in pages the request no longer
+// holds). The block-table entries of all of a thread's rows are fetched first, in one batch
+// of independent loads, and serve both the key and the value copy: looked up row by row, each
+// copy would wait a full memory round trip for its page id.
 template <int HEAD_DIM>
-__device__ __forceinline__ void load_tile(unsigned char* dst, const __nv_bfloat16* arena,
-                                          const int* table, const FlashParams& p, int kv_head,
-                                          int tile_start, int lo, int hi) {
+__device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v_dst, const int* table,
+                                          const FlashParams& p, int kv_head, int tile_start, int lo, int hi) {
   constexpr int kChunks = HEAD_DIM / 8;
   constexpr int kRowsPerPass = kFlashThreads / kChunks;
+  constexpr int kPasses = kTileKeys / kRowsPerPass;
   const int chunk = threadIdx.x % kChunks;
   const int row0 = threadIdx.x / kChunks;
   const int page_size = p.page_mask + 1;
+  if (page_size >= kTileKeys) {
+    // The whole tile lies in one page (tiles start at multiples of 64 and the page size is a
+    // power of two): one table entry, then a fixed stride from row to row.
+    const bool any = tile_start + kTileKeys - 1 >= lo && tile_start <= hi;
+    const int page = any ? __ldg(table + (tile_start >> p.page_shift)) : 0;
+    const bool page_ok = page >= 0 && page < p.num_pages;
+    if (any && !page_ok) atomicOr(p.err, ERRBIT_BAD_PAGE);
+    const int64_t base = page_ok ? ((static_cast<int64_t>(page) * p.kv_heads + kv_head) * page_size +
+                                    (tile_start & p.page_mask) + row0) * HEAD_DIM + chunk * 8
+                                 : 0;
 #pragma unroll
-  for (int pass = 0; pass < kTileKeys / kRowsPerPass; ++pass) {
+    for (int pass = 0; pass < kPasses; ++pass) {
+      const int row = row0 + pass * kRowsPerPass;
+      const int key = tile_start + row;
+      const bool valid = page_ok && key >= lo && key <= hi;
+      const int64_t offset = valid ? base + static_cast<int64_t>(pass) * kRowsPerPass * HEAD_DIM : 0;
+      cp_async_16(smem_u32(k_dst + tile_offset<HEAD_DIM>(row, chunk)), p.k_arena + offset, valid);
+      cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset, valid);
+    }
+    return;
+  }
+  int pages[kPasses];
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
+    const int key = tile_start + row0 + pass * kRowsPerPass;
+    pages[pass] = (key >= lo && key <= hi) ? __ldg(table + (key >> p.page_shift)) : -1;
+  }
+#pragma unroll
+  for (int pass = 0; pass < kPasses; ++pass) {
     const int row = row0 + pass * kRowsPerPass;
     const int key = tile_start + row;
-    bool valid = key >= lo && key <= hi;
-    const __nv_bfloat16* src = arena;
-    if (valid) {
-      const int page = table[key >> p.page_shift];
-      if (page < 0 || page >= p.num_pages) {
-        atomicOr(p.err, ERRBIT_BAD_PAGE);
-        valid = false;
-      } else {
-        src = arena + ((static_cast<int64_t>(page) * p.kv_heads + kv_head) * page_size +
-                       (key & p.page_mask)) * HEAD_DIM + chunk * 8;
-      }
-    }
-    cp_async_16(smem_u32(dst + tile_offset<HEAD_DIM>(row, chunk)), src, valid);
+    const bool in_range = key >= lo && key <= hi;
+    const int page = pages[pass];
+    bool valid = in_range && page >= 0 && page < p.num_pages;
+    if (in_range && !valid) atomicOr(p.err, ERRBIT_BAD_PAGE);
+    const int64_t offset = valid ? ((static_cast<int64_t>(page) * p.kv_heads + kv_head) * page_size +
+                                    (key & p.page_mask)) * HEAD_DIM + chunk * 8
+                                 : 0;
+    cp_async_16(smem_u32(k_dst + tile_offset<HEAD_DIM>(row, chunk)), p.k_arena + offset, valid);
+    cp_async_16(smem_u32(v_dst + tile_offset<HEAD_DIM>(row, chunk)), p.v_arena + offset, valid);
   }
 }
 
@@ -200,8 +226,8 @@ paged_flash_attention_kernel(const FlashParams p) {
   // slot of the ring gets its own commit group, empty if the range is shorter.
   auto fetch = [&](int it) {
     const int slot = it % kRing;
-    load_tile<HEAD_DIM>(k_tiles + slot * kTileBytes, p.k_arena, table, p, kv_head, (tile_begin + it) * kTileKeys, lo, hi);
-    load_tile<HEAD_DIM>(v_tiles + slot * kTileBytes, p.v_arena, table, p, kv_head, (tile_begin + it) * kTileKeys, lo, hi);
+    load_tile<HEAD_DIM>(k_tiles + slot * kTileBytes, v_tiles + slot * kTileBytes, table, p, kv_head,
+                        (tile_begin + it) * kTileKeys, lo, hi);
   };
   int issued = 0;
   if (DECODE) {
@@ -312,12 +338,15 @@ paged_flash_attention_kernel(const FlashParams p) {
       }
       l0 = l0 * alpha0 + sum0;
       l1 = l1 * alpha1 + sum1;
+      // Rescale the running output only when some row's maximum moved (the whole warp decides).
+      if (__any_sync(0xffffffffu, alpha0 != 1.f || alpha1 != 1.f)) {
 #pragma unroll
-      for (int i = 0; i < kDimTiles; ++i) {
-        o[i][0] *= alpha0;
-        o[i][1] *= alpha0;
-        o[i][2] *= alpha1;
-        o[i][3] *= alpha1;
+        for (int i = 0; i < kDimTiles; ++i) {
+          o[i][0] *= alpha0;
+          o[i][1] *= alpha0;
+          o[i][2] *= alpha1;
+          o[i][3] *= alpha1;
+        }
       }
       // O += P V over the warp's keys, 16 at a time.
       {

@@ -282,7 +282,7 @@ def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int) -> int:
     of their partial results stays cheap."""
     tiles = max(1, (max_kv_len + 63) // 64)
     pairs = max(1, num_seqs * kv_heads)
-    want = -(-6 * NUM_SMS // pairs)
+    want = 6 * NUM_SMS // pairs  # rounded down: one block too many would start a third wave
     return max(1, min(tiles, 16, want))
 
 
