@@ -94,18 +94,18 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
         return "stream" if stream else None
     if choice == "skinny":
         return "skinny" if skinny else None
-    # auto, from measurements on a B200 (graph-timed, weights from HBM): for up to 16 rows the
-    # mma.sync kernel wins on small matrices, whose time is all launch and ramp, and the
-    # tcgen05 kernel on large ones (long K or very many rows of W); with more rows of X the
-    # vendor library's tiles serve the mid-sized matrices better.
+    # auto, from measurements on a B200 (graph-timed, weights from HBM, 1.5B shape): for up to
+    # 16 rows the mma.sync kernel wins on small matrices, whose time is all launch and ramp
+    # (3.0 vs 5.1 us for the 6 MB q/k/v product), and the tcgen05 kernel on large ones (down
+    # 11.4 vs 14.1 us, output head 74 vs 107 us; vendor library 16.8 and 78 us). With more
+    # rows the vendor library's tiles are a little faster than either (64 rows: down 13.3 vs
+    # 14.7 us, output head 84 vs 89 us), so it keeps those.
+    if m > 16:
+        return None
     weight_bytes = 2 * n * k
-    if m <= 16:
-        if skinny and weight_bytes < (16 << 20):
-            return "skinny"
-        return "stream" if stream else ("skinny" if skinny else None)
-    if stream and (weight_bytes >= (256 << 20) or (n <= 2048 and k >= 4096)):
-        return "stream"
-    return None
+    if skinny and weight_bytes < (16 << 20):
+        return "skinny"
+    return "stream" if stream else ("skinny" if skinny else None)
 
 
 def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
