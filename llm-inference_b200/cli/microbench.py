@@ -155,12 +155,15 @@ def bench_attention(args, decode: bool) -> dict:
     values = torch.randn_like(keys)
     positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
     token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
-    ctx = make_ctx(positions, token_seq, starts, runs, {"attention": "plain" if args.plain else "auto"})
+    ctx = make_ctx(positions, token_seq, starts, runs, {"attention": "plain" if args.plain else args.attention})
     q = torch.randn(len(positions), q_heads * dim, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
     view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, args.window)
     fn = lambda: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5)
-    us = time_launches(fn, args.iters)
+    # --rotate: back to back inside a CUDA graph, so that neither the host's launch cost nor
+    # the idle gap before a lone launch enters (the cache stays in L2, as it does in a model
+    # step, where the layer's keys were written just before).
+    us = time_back_to_back([fn], 16) if args.rotate else time_launches(fn, args.iters)
     kv_bytes = sum(lens) * kv_heads * dim * 2 * 2
     flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs))
     return {"kernel": "decode_attention" if decode else "prefill_attention", "batch": len(lens), "context": args.context,
@@ -187,6 +190,7 @@ def main(argv=None) -> int:
     parser.add_argument("--page", type=int, default=64)
     parser.add_argument("--window", type=int, default=0)
     parser.add_argument("--plain", action="store_true")
+    parser.add_argument("--attention", default="auto", choices=["auto", "flash", "tcgen05"])
     parser.add_argument("--iters", type=int, default=20)
     args = parser.parse_args(argv)
     if args.library:

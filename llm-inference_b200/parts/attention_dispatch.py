@@ -1,9 +1,12 @@
 """Chooses the attention kernel for a step.
 
-In bfloat16, with a head size and page size the tensor-core kernel takes, the step's
-single-token requests (which lead the batch) go to its split-key decode form and the prompt
-portions to its prefill form. Everything else - float32, other head sizes, pages whose size
-is no power of two - runs the plain kernel, which takes every shape.
+In bfloat16, with a head size and page size the tensor-core kernels take, the step's
+single-token requests (which lead the batch) go to the split-key decode kernel (mma.sync) and
+the prompt portions to the tcgen05 / TMEM kernel (head_dim 128, pages of at least 16 rows) or
+else to the mma.sync prefill form. Everything else - float32, other head sizes, pages whose
+size is no power of two - runs the plain kernel, which takes every shape.
+``options["attention"]``: ``"auto"``, ``"plain"``, ``"flash"`` (mma.sync only) or
+``"tcgen05"`` (refuse shapes the tcgen05 kernel does not take).
 """
 
 from __future__ import annotations
@@ -31,8 +34,8 @@ def attend(
         and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, cache.page_size, decode=False)
     )
     if not tuned:
-        if choice == "flash":
-            raise ops.KernelError("the tensor-core attention kernel does not take this shape or dtype")
+        if choice in ("flash", "tcgen05"):
+            raise ops.KernelError("the tensor-core attention kernels do not take this shape or dtype")
         ops.paged_attention_plain(ctx, cache, q, out, q_heads, kv_heads, head_dim, scale)
         return
     decode_seqs = ctx.num_decode_seqs
@@ -45,7 +48,16 @@ def attend(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits,
         )
-    if ctx.num_seqs > decode_seqs:
+    if ctx.num_seqs > decode_seqs and choice in ("auto", "tcgen05") and ops.prefill_tcgen05_supported(
+        ctx, q_heads, kv_heads, head_dim, cache.page_size, ctx.max_kv_len
+    ):
+        ops.paged_prefill_attention_tcgen05(
+            ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
+            first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, max_q_len=ctx.max_q_len,
+        )
+    elif ctx.num_seqs > decode_seqs:
+        if choice == "tcgen05":
+            raise ops.KernelError("the tcgen05 attention kernel does not take this shape")
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=decode_seqs, num_seqs=ctx.num_seqs - decode_seqs, decode=False, max_q_len=ctx.max_q_len,

@@ -328,6 +328,38 @@ def paged_flash_attention(
     return out
 
 
+def prefill_tcgen05_supported(ctx: StepContext, q_heads: int, kv_heads: int, head_dim: int, page_size: int, max_kv_len: int) -> bool:
+    return bool(ctx.lib.lib.b200_flash_prefill_tcgen05_supported(q_heads, kv_heads, head_dim, page_size, max_kv_len))
+
+
+def paged_prefill_attention_tcgen05(
+    ctx: StepContext,
+    cache: CacheView,
+    q: torch.Tensor,
+    out: torch.Tensor,
+    q_heads: int,
+    kv_heads: int,
+    head_dim: int,
+    scale: float,
+    *,
+    first_seq: int,
+    num_seqs: int,
+    max_q_len: int,
+) -> torch.Tensor:
+    """Prompt-portion attention on tcgen05 / TMEM for requests ``first_seq ..`` of the step."""
+    if num_seqs <= 0:
+        return out
+    _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.keys.dtype == torch.bfloat16, "tcgen05 attention is bfloat16 only")
+    _need(q.is_contiguous() and out.is_contiguous() and cache.keys.is_contiguous() and cache.values.is_contiguous(), "tcgen05 attention: operands must be contiguous")
+    ctx.lib.call(
+        "b200_flash_prefill_tcgen05", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
+        ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs), c_int(max_q_len),
+        c_int(ctx.max_kv_len), c_int(cache.max_pages), c_int(cache.num_pages), c_int(q_heads), c_int(kv_heads),
+        c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale), ptr(ctx.err), ctx.stream,
+    )
+    return out
+
+
 def _offset(tensor: torch.Tensor, nbytes: int):
     from ctypes import c_void_p
 

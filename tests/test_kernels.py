@@ -461,6 +461,40 @@ def test_paged_flash_attention(lib, case):
     assert int(ctx.err.item()) == 0
 
 
+TCGEN05_CASES = [
+    # q_heads, kv_heads, head_dim, page, window, starts, runs
+    (12, 2, 128, 64, 0, [0], [300]),
+    (12, 2, 128, 16, 0, [0, 17, 300], [70, 130, 5]),
+    (28, 4, 128, 64, 0, [0, 1000], [200, 3]),
+    (40, 8, 128, 32, 0, [64, 63, 129], [3, 2, 40]),
+    (8, 8, 128, 16, 100, [90, 0], [1, 260]),
+    (4, 1, 128, 128, 0, [500, 3], [20, 400]),
+    (6, 2, 128, 64, 50, [0, 100], [260, 60]),
+]
+
+
+@pytest.mark.parametrize("case", TCGEN05_CASES)
+def test_prefill_attention_on_tcgen05(lib, case):
+    from llm_inference_b200.parts import attention_dispatch
+    from llm_inference_b200.parts.context import CacheView
+
+    q_heads, kv_heads, head_dim, page, window, starts, runs = case
+    q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+        torch.bfloat16, q_heads, kv_heads, head_dim, page, window, starts, runs, seed=13
+    )
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
+    ctx.options["attention"] = "tcgen05"
+    ctx.num_decode_seqs = 0  # every request through the prefill kernel, one-token runs too
+    # The block table pads rows with a real page (the engine pads with the arena's spare page).
+    tables = np.where(tables < 0, num_pages - 1, tables).astype(np.int32)
+    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+    out = torch.full_like(q, float("nan"))
+    attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, head_dim, head_dim**-0.5)
+    torch.cuda.synchronize()
+    assert int(ctx.err.item()) == 0
+    torch.testing.assert_close(out.double(), expected, **tol(torch.bfloat16))
+
+
 def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(lib):
     from llm_inference_b200.parts import attention_dispatch
     from llm_inference_b200.parts.context import CacheView
