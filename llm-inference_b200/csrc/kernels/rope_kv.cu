@@ -8,6 +8,8 @@
 // (python/instinct/paged_kv.py:259-265).
 #include "common.cuh"
 
+constexpr int kWideTokens = 64;  // from this many tokens on, one block per token (below)
+
 // One block per (token, head): query heads first, then key heads, then value heads. Thread i
 // handles pair slot i of its head (see below), so a decode step spreads over
 // tokens * (q_heads + 2 * kv_heads) small blocks instead of one block per token.
@@ -81,6 +83,102 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
   }
 }
 
+// The same work for many tokens (prompt portions): one block per token. The token's sines and
+// cosines are computed once into shared memory and shared by all its heads, and every thread
+// moves two adjacent dims at a time (one 32-bit access for bfloat16). Full rotation only
+// (rot == head_dim, head_dim a multiple of 4); the arithmetic per element is that of the
+// kernel above.
+template <typename T>
+struct Pair;
+template <>
+struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <>
+struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __nv_bfloat162(__float2bfloat16_rn(a), __float2bfloat16_rn(b));
+  }
+};
+
+template <typename T>
+__global__ void rope_kv_write_wide_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+                                          const float* __restrict__ inv_freq,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ token_seq,
+                                          const int* __restrict__ block_table, int max_pages,
+                                          int num_pages, T* __restrict__ k_arena,
+                                          T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
+                                          int kv_heads, int head_dim, int page_size, int write_kv,
+                                          int* __restrict__ err) {
+  extern __shared__ float angles[];  // cos[half], sin[half]
+  wait_for_predecessor();
+  let_successor_start();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = head_dim / 2;
+  for (int slot = threadIdx.x; slot < half; slot += blockDim.x) {
+    float sn, cs;
+    sincosf(static_cast<float>(pos) * inv_freq[slot], &sn, &cs);
+    angles[slot] = cs;
+    angles[half + slot] = sn;
+  }
+  int64_t kv_row = -1;
+  if (write_kv) {
+    const int logical = pos / page_size;
+    if (pos < 0 || logical >= max_pages) {
+      if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_POSITION);
+    } else {
+      const int page = block_table[static_cast<int64_t>(token_seq[t]) * max_pages + logical];
+      if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
+      } else {
+        kv_row = kv_row_offset(page, 0, pos % page_size, kv_heads, page_size, head_dim);
+      }
+    }
+  }
+  __syncthreads();
+  const int rotated_heads = q_heads + kv_heads;
+  const int heads = write_kv ? q_heads + 2 * kv_heads : q_heads;
+  const int pairs = half / 2;  // pairs of adjacent slots per head
+  const int width = (q_heads + 2 * kv_heads) * head_dim;
+  const T* row = qkv + static_cast<int64_t>(t) * width;
+  const int64_t head_stride = static_cast<int64_t>(page_size) * head_dim;  // between kv heads of a page
+  for (int item = threadIdx.x; item < heads * pairs; item += blockDim.x) {
+    const int head = item / pairs, slot = 2 * (item - head * pairs);
+    T* dst;
+    if (head < q_heads) {
+      dst = q_out + (static_cast<int64_t>(t) * q_heads + head) * head_dim;
+    } else {
+      if (kv_row < 0) continue;
+      const bool is_k = head < rotated_heads;
+      dst = (is_k ? k_arena : v_arena) + kv_row + (is_k ? head - q_heads : head - rotated_heads) * head_stride;
+    }
+    const T* src = row + head * head_dim;
+    float2 lo = Pair<T>::load(src + slot), hi = Pair<T>::load(src + half + slot);
+    if (bias) {
+      const float* b = bias + head * head_dim;
+      lo.x += b[slot];
+      lo.y += b[slot + 1];
+      hi.x += b[half + slot];
+      hi.y += b[half + slot + 1];
+    }
+    if (head < rotated_heads) {
+      const float c0 = angles[slot], c1 = angles[slot + 1], s0 = angles[half + slot], s1 = angles[half + slot + 1];
+      const float a0 = lo.x * c0 - hi.x * s0, b0 = hi.x * c0 + lo.x * s0;
+      const float a1 = lo.y * c1 - hi.y * s1, b1 = hi.y * c1 + lo.y * s1;
+      lo = make_float2(a0, a1);
+      hi = make_float2(b0, b1);
+    }
+    Pair<T>::store(dst + slot, lo.x, lo.y);
+    Pair<T>::store(dst + half + slot, hi.x, hi.y);
+  }
+}
+
 B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float* inv_freq,
                                 const int* positions, const int* token_seq,
                                 const int* block_table, int max_pages, int num_pages,
@@ -94,6 +192,25 @@ B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float*
   B200_REQUIRE(rot >= 0 && rot <= head_dim && rot % 2 == 0,
                "rope_kv_write: rotary dims %d must be even and at most head_dim %d", rot, head_dim);
   B200_REQUIRE(page_size > 0 && max_pages > 0, "rope_kv_write: bad page geometry");
+  if (tokens >= kWideTokens && rot == head_dim && head_dim % 4 == 0) {
+    const size_t angles = static_cast<size_t>(head_dim) * sizeof(float);
+    const dim3 wide_grid(tokens), wide_block(256);
+    if (dtype == DTYPE_F32) {
+      launch_kernel(rope_kv_write_wide_kernel<float>, wide_grid, wide_block, angles, stream,
+          static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+          max_pages, num_pages, static_cast<float*>(k_arena), static_cast<float*>(v_arena),
+          static_cast<float*>(q_out), q_heads, kv_heads, head_dim, page_size, write_kv, err);
+    } else if (dtype == DTYPE_BF16) {
+      launch_kernel(rope_kv_write_wide_kernel<__nv_bfloat16>, wide_grid, wide_block, angles, stream,
+          static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+          max_pages, num_pages, static_cast<__nv_bfloat16*>(k_arena),
+          static_cast<__nv_bfloat16*>(v_arena), static_cast<__nv_bfloat16*>(q_out), q_heads,
+          kv_heads, head_dim, page_size, write_kv, err);
+    } else {
+      return b200_fail("rope_kv_write: unknown dtype %d", dtype);
+    }
+    return b200_check_launch("rope_kv_write");
+  }
   const int threads = head_dim >= 128 ? 64 : 32;
   const size_t smem = 0;
   const dim3 grid(tokens, q_heads + 2 * kv_heads);

@@ -83,7 +83,7 @@ def test_embedding_gather(lib, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden", [1000, 96, 4104])
+@pytest.mark.parametrize("hidden", [1000, 96, 4104, 1001, 8200])  # 16-byte form, and rows it does not take
 def test_rmsnorm_with_and_without_the_residual_add(lib, dtype, hidden):
     from llm_inference_b200.parts import ops
 
@@ -237,13 +237,14 @@ def gather_cache(arena, table, length, page_size):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("runs", [[1, 9, 3], [1, 70, 33]], ids=["few", "many"])  # "many": the one-block-per-token form
 @pytest.mark.parametrize("q_heads,kv_heads,head_dim,rot,page", [(4, 2, 16, 16, 4), (6, 1, 48, 32, 8), (5, 5, 128, 128, 16)])
-def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page):
+def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page, runs):
     from llm_inference_b200.parts import ops
     from llm_inference_b200.parts.context import CacheView
 
     torch.manual_seed(4)
-    starts, runs = [37, 0, 5], [1, 9, 3]  # a decoded token, a fresh prompt, a later portion
+    starts = [37, 0, 5]  # a decoded token, a fresh prompt, a later portion
     seq_lens = [s + r for s, r in zip(starts, runs)]
     tables, num_pages = paged_layout(seq_lens, page)
     positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
