@@ -205,6 +205,7 @@ PYBIND11_MODULE(b200_host, m) {
       .def("commit", &Scheduler::commit)
       .def("abandon", &Scheduler::abandon)
       .def("draw_key", &Scheduler::draw_key)
+      .def("repeats", &Scheduler::repeats)
       .def_property_readonly("max_model_length", &Scheduler::max_model_length)
       .def("stats", [](const Scheduler& s) {
         const SchedulerStats t = s.stats();

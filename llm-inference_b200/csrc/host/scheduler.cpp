@@ -218,6 +218,20 @@ void Scheduler::abandon(const Plan& plan) {
   }
 }
 
+bool Scheduler::repeats(const Plan& plan) const {
+  if (plan.entries.empty() || !waiting_.empty() || plan.entries.size() != running_.size()) return false;
+  for (const auto& e : plan.entries) {
+    if (!e.decode || e.count != 1 || !e.wants_token) return false;
+    auto it = requests_.find(e.id);
+    if (it == requests_.end()) return false;
+    const Request& r = it->second;
+    if (r.state != SequenceState::running || !r.forced.empty()) return false;
+    if (static_cast<int>(r.output.size()) + 1 >= r.max_new_tokens) return false;  // ends by length
+    if (e.start + 2 >= max_model_length_) return false;                           // ends by context
+  }
+  return true;
+}
+
 std::uint64_t Scheduler::draw_key(RequestId id) const {
   const Request& r = request(id);
   const __int128 modulus = static_cast<__int128>(1) << 63;

@@ -105,6 +105,12 @@ class Scheduler {
   // Key of the uniform draw for the request's next token: (seed * 1000003 + generated) mod 2^63
   // (python/instinct/sampling.py:94-98).
   std::uint64_t draw_key(RequestId id) const;
+  // True when the step after `plan` is bound to feed the same requests one token each, unless
+  // a token sampled in this step ends one of them: every entry is a running request's single
+  // token, no request waits for admission or is still reading its prompt, none reaches its
+  // length or context limit with this step's token, and none has a forced token pending.
+  // The engine may then launch that next step before it has read this step's tokens.
+  bool repeats(const Plan& plan) const;
 
   SchedulerStats stats() const;
   int max_model_length() const { return max_model_length_; }

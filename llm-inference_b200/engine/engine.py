@@ -97,6 +97,7 @@ class Engine:
         seed: int = 0,
         num_pages: int | None = None,
         cuda_graphs: bool = True,
+        run_ahead: bool = True,
         model: Model | None = None,
     ) -> None:
         if max_num_sequences <= 0 or kv_cache_bytes <= 0 or page_size <= 0:
@@ -143,6 +144,12 @@ class Engine:
             options={"cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens},
         )
         self.sampler = Sampler(self.device, max_num_sequences)
+        # While a decode step's tokens travel to the host, the next step may already run (see
+        # ModelRunner.step_ahead); `run_ahead=False` keeps every step behind the host.
+        self.run_ahead = bool(run_ahead) and self.runner.use_graphs
+        self._ahead = None
+        self.steps_ahead_used = 0
+        self.steps_ahead_dropped = 0
         self._host = host()
         self.scheduler = self._host.Scheduler(
             self.cache.manager,
@@ -207,37 +214,65 @@ class Engine:
         plan = self.scheduler.plan()
         self.cache.clear_new_slots()
         entries = plan.entries
+        ahead, self._ahead = self._ahead, None
         if not entries:
             return []
         try:
             tokens = plan.tokens
-            batch = [
-                StepEntry(
-                    e.request_id,
-                    tokens[e.token_offset : e.token_offset + e.count],
-                    (e.count - 1,) if e.wants_token else (),
-                )
-                for e in entries
-            ]
-            logits = self.runner.step(batch)
+            if ahead is not None and self._is_this_step(ahead, plan, tokens):
+                logits = self.runner.accept_ahead(ahead)
+                self.steps_ahead_used += 1
+            else:
+                if ahead is not None:
+                    self.steps_ahead_dropped += 1
+                batch = [
+                    StepEntry(
+                        e.request_id,
+                        tokens[e.token_offset : e.token_offset + e.count],
+                        (e.count - 1,) if e.wants_token else (),
+                    )
+                    for e in entries
+                ]
+                logits = self.runner.step(batch)
             wanting = [e for e in entries if e.wants_token]
             if wanting:
                 requests = [self.scheduler.request(e.request_id) for e in wanting]
-                chosen, err = self.sampler.sample(
+                rows = self.sampler.launch(
                     logits,
                     [r.sampling for r in requests],
                     [self.scheduler.draw_key(r.request_id) for r in requests],
                     self.runner.err,
                 )
+                if self.run_ahead and self.scheduler.repeats(plan):
+                    # The next step will feed these tokens to the same requests unless one of
+                    # them ends a request: launch it now, behind the sampling kernels.
+                    self._ahead = self.runner.step_ahead([e.request_id for e in entries], self.sampler.tokens_device)
+                chosen, err = self.sampler.result(rows)
                 if err:
                     check_error_word(self.runner.err, "step")
             else:
                 chosen = []
             events = self.scheduler.commit(plan, chosen)
+            if self._ahead is not None:
+                emitted = {e.request_id: e.token for e in events}
+                self._ahead.tokens = [emitted.get(r) for r in self._ahead.request_ids]
         except Exception:
+            self._ahead = None
             self.scheduler.abandon(plan)
             raise
         return [TokenEvent(e.request_id, e.token, e.finished, e.reason) for e in events]
+
+    def _is_this_step(self, ahead, plan, tokens) -> bool:
+        """Whether the step launched ahead fed exactly what ``plan`` asks for now."""
+        entries = plan.entries
+        if ahead.issue != self.runner.issue or ahead.tokens is None or len(entries) != len(ahead.request_ids):
+            return False
+        for e, request_id, start, token in zip(entries, ahead.request_ids, ahead.starts, ahead.tokens):
+            if e.request_id != request_id or e.count != 1 or not e.wants_token or e.start != start:
+                return False
+            if int(tokens[e.token_offset]) != token:
+                return False
+        return True
 
     def generate(
         self,
@@ -295,6 +330,8 @@ class Engine:
             "max_model_length": self.max_model_length,
             "page_size": self.page_size,
             "model_steps": self.runner.steps,
+            "steps_ahead_used": self.steps_ahead_used,
+            "steps_ahead_dropped": self.steps_ahead_dropped,
             "weight_bytes": self.model.weight_bytes(),
         }
         out.update(self.scheduler.stats())
@@ -315,6 +352,8 @@ class Engine:
         stats = self.scheduler.stats()
         for request_id in range(1, int(stats["submitted"]) + int(stats["rejected"]) + 1):
             self.scheduler.cancel(request_id)
+        self._ahead = None
+        torch.cuda.synchronize(self.device)  # a step launched ahead may still be running
         self._closed = True
 
     def __enter__(self) -> "Engine":

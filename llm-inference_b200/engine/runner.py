@@ -32,6 +32,18 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)
 
 
+@dataclass
+class AheadStep:
+    """A decode step launched before the step before it had been read back (see
+    :meth:`ModelRunner.step_ahead`): who was in it, where each request stood, and its logits."""
+
+    request_ids: list[int]
+    starts: list[int]
+    logits: torch.Tensor
+    issue: int
+    tokens: list[int] | None = None  # what it was fed, once the host knows
+
+
 class _Staging:
     """Host (pinned) and device int32 buffers the step's metadata travels in, as one copy."""
 
@@ -119,6 +131,7 @@ class ModelRunner:
         self._graph_generation = -1
         self.graph_replays = 0
         self.launches_per_graph: dict[int, int] = {}
+        self.issue = 0  # batches launched so far; an AheadStep is only good while nothing followed it
 
     # ------------------------------------------------------------------------------------------
 
@@ -169,10 +182,59 @@ class ModelRunner:
         for e, start in zip(entries, starts):
             manager.advance(e.request_id, start + len(e.tokens))
         self.steps += 1
+        self.issue += 1
         self.tokens_run += total
         if check:
             self.check()
         return logits
+
+    # -- a decode step launched ahead of its tokens -------------------------------------------------
+    #
+    # Between two decode steps the device would wait for the host: the sampled tokens travel to
+    # the host, the scheduler decides, the next step's metadata travels back. When the next step
+    # is known to feed the same requests one token each, everything about it except the token
+    # ids is known already, and the ids are on the device. `step_ahead` launches that step with
+    # the ids copied device to device, behind the sampling kernels, so it runs while the host
+    # catches up. Nothing is committed: the cache lengths stay where they are until
+    # `accept_ahead`; a step that turns out not to be wanted (a request ended, another was
+    # admitted) is simply never accepted. What it wrote are keys and values at positions that
+    # either will be rewritten with the same numbers or belong to a request that is gone.
+
+    def step_ahead(self, request_ids: Sequence[int], tokens_dev: torch.Tensor) -> AheadStep | None:
+        """Launch one token per request, the tokens being ``tokens_dev[:len(request_ids)]`` on
+        the device. Returns None, launching nothing, unless the step can replay a captured
+        graph."""
+        count = len(request_ids)
+        if not self.use_graphs or count == 0 or count > self.cache.max_num_sequences:
+            return None
+        bucket = self._bucket(count)
+        cached = self._graphs.get(bucket)
+        if cached is None or self._graph_generation != self.workspace.generation:
+            return None
+        manager = self.cache.manager
+        starts = [manager.length(r) for r in request_ids]
+        if any(start + 1 > self.cache.max_pages_per_request * self.cache.page_size for start in starts):
+            return None
+        for r, start in zip(request_ids, starts):
+            manager.ensure(r, start + 1)
+        self._build_context([StepEntry(r, (0,)) for r in request_ids], starts, list(range(bucket)), pad_to=bucket)
+        self.staging.dev[:count].copy_(tokens_dev[:count], non_blocking=True)  # the token ids lead the buffer
+        graph, logits, _ = cached
+        graph.replay()
+        self.graph_replays += 1
+        self.issue += 1
+        return AheadStep(list(request_ids), starts, logits[:count], self.issue)
+
+    def accept_ahead(self, ahead: AheadStep) -> torch.Tensor:
+        """The step launched ahead is the step wanted now: count it and return its logits."""
+        if ahead.issue != self.issue:
+            raise RuntimeError("another batch ran after the step launched ahead")
+        manager = self.cache.manager
+        for r, start in zip(ahead.request_ids, ahead.starts):
+            manager.advance(r, start + 1)
+        self.steps += 1
+        self.tokens_run += len(ahead.request_ids)
+        return ahead.logits
 
     def check(self) -> None:
         """Raise if any kernel flagged an error since the last check (synchronises)."""

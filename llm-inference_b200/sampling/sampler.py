@@ -25,6 +25,12 @@ class Sampler:
         self._dev = torch.empty(max_rows * 8, dtype=torch.int32, device=device)
         self._tokens = torch.zeros(max_rows + 1, dtype=torch.int32, device=device)
         self._tokens_host = torch.zeros(max_rows + 1, dtype=torch.int32, pin_memory=True)
+        self._done = torch.cuda.Event()  # recorded after the copy of a step's tokens to the host
+
+    @property
+    def tokens_device(self) -> torch.Tensor:
+        """The last launch's tokens on the device, row by row (valid in stream order)."""
+        return self._tokens
 
     def sample(
         self,
@@ -35,11 +41,17 @@ class Sampler:
     ) -> tuple[list[int], int]:
         """One token per row of ``logits`` (``[rows, vocab]`` float32). ``keys[i]`` seeds
         row i's draw. Returns the tokens and the kernels' error word (0 = none)."""
+        return self.result(self.launch(logits, params, keys, err))
+
+    def launch(self, logits: torch.Tensor, params: Sequence, keys: Sequence[int], err: torch.Tensor | None = None) -> int:
+        """Enqueue the kernels of :meth:`sample` and the copy of their tokens to the host;
+        returns the number of rows for :meth:`result`. Work enqueued after this call does not
+        delay the result."""
         rows, vocab = logits.shape
         if rows > self.max_rows:
             raise ValueError(f"{rows} rows to sample, the sampler was sized for {self.max_rows}")
         if rows == 0:
-            return [], 0
+            return 0
         stream = torch.cuda.current_stream(self.device).cuda_stream
         from ctypes import c_void_p
 
@@ -80,6 +92,13 @@ class Sampler:
         else:
             tokens[rows : rows + 1].zero_()
         self._tokens_host[: rows + 1].copy_(tokens[: rows + 1], non_blocking=True)
-        torch.cuda.current_stream(self.device).synchronize()
+        self._done.record()
+        return rows
+
+    def result(self, rows: int) -> tuple[list[int], int]:
+        """Wait for the tokens of the last :meth:`launch` (and only for them)."""
+        if rows == 0:
+            return [], 0
+        self._done.synchronize()
         out = self._tokens_host[: rows + 1].tolist()
         return out[:rows], out[rows]

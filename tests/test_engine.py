@@ -196,3 +196,59 @@ def test_requests_wait_when_pages_run_out(tiny):
         assert drained(engine)
         with pytest.raises(ValueError, match="more K/V memory than the cache has"):
             engine.submit([1] * 100, 20)
+
+
+def test_steps_launched_ahead_change_nothing(tiny):
+    """With `run_ahead` a decode step is launched before the previous step's tokens reach the
+    host. A request that ends on a stop token, one that is cancelled, one submitted late and a
+    forced token all make such a step unwanted; the tokens must be those of an engine that
+    never runs ahead, and those of the plain implementation."""
+    name, folder, config, weights = tiny
+    rng = np.random.default_rng(11)
+    vocab = config["vocab_size"]
+    prompts = [random_tokens(rng, vocab, n) for n in (5, 9, 3, 12)]
+    long = plain.greedy(config, weights, prompts[0], 40)
+    stop = long[17]  # request 0 ends on this token (its first occurrence decides where)
+
+    def scenario(run_ahead: bool):
+        with engine_for(name, folder, run_ahead=run_ahead) as engine:
+            a = engine.submit(prompts[0], 40, [stop])
+            b = engine.submit(prompts[1], 33)
+            c = engine.submit(prompts[2], 50)
+            steps = 0
+            late = None
+            while engine.has_work():
+                engine.step()
+                steps += 1
+                if steps == 12:
+                    engine.cancel(c)
+                if steps == 20:
+                    late = engine.submit(prompts[3], 14)
+                if steps == 25:
+                    engine.force(b, [1])
+            outputs = [list(engine.request(r).output) for r in (a, b, c, late)]
+            stats = engine.stats()
+            assert drained(engine)
+        return outputs, stats
+
+    with_ahead, stats = scenario(True)
+    without, stats_without = scenario(False)
+    assert with_ahead == without
+    assert stats_without["steps_ahead_used"] == 0 and stats_without["steps_ahead_dropped"] == 0
+    assert stats["steps_ahead_used"] > 10 and stats["steps_ahead_dropped"] >= 1
+    assert with_ahead[0] == long[: long.index(stop) + 1]
+    assert with_ahead[3] == plain.greedy(config, weights, prompts[3], 14)
+
+
+def test_sampled_tokens_do_not_depend_on_running_ahead(tiny):
+    name, folder, config, _ = tiny
+    rng = np.random.default_rng(12)
+    prompts = [random_tokens(rng, config["vocab_size"], n) for n in (4, 11)]
+    from llm_inference_b200 import SamplingParams
+
+    options = dict(sampling=SamplingParams(temperature=0.9, top_k=20, top_p=0.95, seed=77))
+    with engine_for(name, folder, run_ahead=True) as engine:
+        ahead = run_all(engine, prompts, 30, **options)
+        assert engine.stats()["steps_ahead_used"] > 10
+    with engine_for(name, folder, run_ahead=False) as engine:
+        assert run_all(engine, prompts, 30, **options) == ahead

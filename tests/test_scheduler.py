@@ -193,3 +193,64 @@ def test_draw_keys_follow_the_seed_and_the_step():
     assert s.draw_key(a) == (12345 * 1_000_003 + 1) % (1 << 63)
     assert s.draw_key(b) != s.draw_key(a)
     assert not s.request(a).sampling.greedy and h.SamplingParams(temperature=0.8, top_k=1).greedy
+
+
+def test_when_the_next_step_repeats_this_one():
+    """`repeats(plan)`: the next plan is bound to feed the same requests one token each (unless
+    a sampled token stops one), which is when the engine may launch that step early."""
+    h = host()
+    cache, s = make(h, context=40)
+    a = s.submit([1] * 5, 8, [], h.SamplingParams())
+    plan = s.plan()
+    assert not s.repeats(plan)  # a prompt portion
+    s.commit(plan, [9])
+    plan = s.plan()
+    assert [e.decode for e in plan.entries] == [True] and s.repeats(plan)
+    s.commit(plan, [9])
+    b = s.submit([2] * 3, 20, [], h.SamplingParams())
+    plan = s.plan()  # a decodes, b reads its prompt
+    assert not s.repeats(plan)
+    s.commit(plan, [9, 9])
+    plan = s.plan()
+    assert [(e.request_id, e.decode) for e in plan.entries] == [(a, True), (b, True)] and s.repeats(plan)
+    s.commit(plan, [9, 9])
+    following = s.plan()
+    assert [(e.request_id, e.start, e.count) for e in following.entries] == [
+        (e.request_id, e.start + 1, 1) for e in plan.entries
+    ]
+    # A forced token and a waiting request say no.
+    s.force(a, [3])
+    assert not s.repeats(following)
+    s.commit(following, [9, 9])
+    plan = s.plan()
+    assert s.repeats(plan)
+    blocked = [s.submit([4] * 3, 2, [], h.SamplingParams()) for _ in range(2)]  # the third sequence, and one that waits
+    assert not s.repeats(plan)
+    s.commit(plan, [9, 9])
+    for r in blocked:
+        s.cancel(r)
+    # So does the last token before a length limit: a has 6 of its 8 tokens, then 7.
+    plan = s.plan()
+    assert len(s.request(a).output) == 6 and s.repeats(plan)
+    s.commit(plan, [9, 9])
+    plan = s.plan()
+    assert len(s.request(a).output) == 7 and not s.repeats(plan)
+    events = s.commit(plan, [9, 9])
+    assert [(e.request_id, e.finished) for e in events] == [(a, True), (b, False)]
+
+
+def test_repeats_stops_before_the_context_limit():
+    h = host()
+    cache, s = make(h, context=9)
+    a = s.submit([1] * 5, 4, [], h.SamplingParams())  # ends where the context does
+    run_step(s)
+    plan = s.plan()  # position 5
+    assert s.repeats(plan)
+    s.commit(plan, [9])
+    plan = s.plan()  # position 6
+    assert s.repeats(plan)
+    s.commit(plan, [9])
+    plan = s.plan()  # position 7: this step's token is the last one
+    assert not s.repeats(plan)
+    events = s.commit(plan, [9])
+    assert events[0].finished and not s.has_work()
