@@ -1,0 +1,71 @@
+"""Layers of the benchmark's size (Qwen2.5-1.5B: 12/2 heads of 128, hidden 1536, intermediate
+8960, vocabulary 151936), three of them with random weights: a 700-token prompt in two
+portions and three decoded tokens, in bfloat16 with each attention kernel, against the 32-bit
+path. The tiny test configurations never reach the tile counts, cluster sizes and split
+factors these sizes do."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": 3, "hidden_size": 1536,
+    "num_attention_heads": 12, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 8960,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "max_position_embeddings": 32768, "eos_token_id": 151643, "max_window_layers": 1,
+}
+
+
+def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto") -> np.ndarray:
+    import torch
+
+    from llm_inference_b200 import models  # noqa: F401  (registers the architecture)
+    from llm_inference_b200.config import parse_config
+    from llm_inference_b200.engine.engine import Engine
+    from llm_inference_b200.engine.loading import random_model
+    from llm_inference_b200.engine.runner import StepEntry
+
+    settings = dict(SHAPE, use_sliding_window=window > 0, sliding_window=window if window else 32768)
+    _, config = parse_config(settings)
+    model = random_model(config, 5, dtype, "cuda:0", std=0.05)
+    engine = Engine(
+        model=model, max_num_sequences=4, max_model_length=2048, kv_cache_bytes=1 << 30, prefill_chunk_size=1024,
+        prefill_burst_size=1024, max_batch_tokens=1100, dtype=dtype, cuda_graphs=False,
+    )
+    engine.runner.options.update(attention=attention, gemm=gemm)
+    prompt = [int(t) for t in np.random.default_rng(0).integers(0, SHAPE["vocab_size"], 700)]
+    engine.cache.open(1)
+    rows = [engine.runner.step([StepEntry(1, prompt[:517], (516,))])]
+    rows.append(engine.runner.step([StepEntry(1, prompt[517:], (len(prompt) - 518,))]))
+    for token in (11, 222, 3333):
+        rows.append(engine.runner.step([StepEntry(1, (token,), (0,))]))
+    engine.runner.check()
+    out = torch.cat(rows).float().cpu().numpy()
+    engine.close()
+    return out
+
+
+@pytest.mark.parametrize("window", [0, 300], ids=["full", "window300"])
+def test_benchmark_sized_layers_in_bfloat16_follow_the_32_bit_path(window):
+    reference = logits_of("float32", "auto", window)
+    scale = float(reference.std())
+    results = {
+        name: logits_of("bfloat16", attention, window, gemm)
+        for name, (attention, gemm) in {
+            "tcgen05": ("tcgen05", "auto"), "flash": ("flash", "auto"), "plain+library": ("plain", "library"),
+        }.items()
+    }
+    for name, got in results.items():
+        error = np.abs(got - reference)
+        # bfloat16 keeps 8 bits: activations rounded a few dozen times on the way cost a few
+        # per cent of the logits' spread, whichever kernels run; a wrong tile costs the spread.
+        assert error.mean() <= 0.03 * scale and error.max() <= 0.2 * scale, (name, error.mean(), error.max(), scale)
+        assert (got.argmax(axis=1) == reference.argmax(axis=1)).all(), name
+    # The engine's own kernels are no further from 32-bit than the library product with the
+    # plain attention kernel is.
+    baseline = np.abs(results["plain+library"] - reference).mean()
+    for name in ("tcgen05", "flash"):
+        assert np.abs(results[name] - reference).mean() <= 1.1 * baseline, name
