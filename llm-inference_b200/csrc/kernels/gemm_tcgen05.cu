@@ -35,6 +35,7 @@ namespace {
 constexpr int kBlockRows = 128;  // rows of W per block = MMA M
 constexpr int kBlockK = 64;      // k per stage: 128 bytes of bf16 = one swizzle row
 constexpr int kMmaK = 16;
+constexpr int kMaxMembers = 16;  // blocks of a cluster that share rows of W
 constexpr int kMaxStages = 12;    // the launcher picks the depth from how many blocks share an SM
 constexpr int kThreadsT = 192;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
@@ -288,10 +289,23 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         for (int item = tid; item < pairs * p.M; item += 128) {
           const int m = item / pairs, j = item - m * pairs;
           const int r = r_begin + 2 * j;
+          // All members' values are requested before the first is used: one round trip through
+          // the cluster's shared memory, not one per member. The sums run in member order.
+          float gates[kMaxMembers], ups[kMaxMembers];
+#pragma unroll
+          for (int rank = 0; rank < kMaxMembers; ++rank) {
+            if (rank < members) {
+              gates[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
+              ups[rank] = load_peer_f32(partial + m * kBlockRows + r + 1, rank);
+            }
+          }
           float gate = 0.f, up = 0.f;
-          for (int rank = 0; rank < members; ++rank) {
-            gate += load_peer_f32(partial + m * kBlockRows + r, rank);
-            up += load_peer_f32(partial + m * kBlockRows + r + 1, rank);
+#pragma unroll
+          for (int rank = 0; rank < kMaxMembers; ++rank) {
+            if (rank < members) {
+              gate += gates[rank];
+              up += ups[rank];
+            }
           }
           const int n = n0 + r;
           if (n < p.N)
@@ -301,8 +315,14 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       } else {
         for (int item = tid; item < rows * p.M; item += 128) {
           const int m = item / rows, r = r_begin + (item - m * rows);
+          float values[kMaxMembers];
+#pragma unroll
+          for (int rank = 0; rank < kMaxMembers; ++rank)
+            if (rank < members) values[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
           float sum = 0.f;
-          for (int rank = 0; rank < members; ++rank) sum += load_peer_f32(partial + m * kBlockRows + r, rank);
+#pragma unroll
+          for (int rank = 0; rank < kMaxMembers; ++rank)
+            if (rank < members) sum += values[rank];
           if (n0 + r < p.N) write_output(p, m, n0 + r, sum);
         }
       }
@@ -372,7 +392,7 @@ StreamPlan plan_stream(int N, int K, int tokens_pad) {
   // 10.6 to 8.6 us with them.
   int widest = plan.blocks * 8 < 148 ? 16 : 8;
   if (const char* forced = getenv("B200_STREAM_MEMBERS")) widest = atoi(forced);
-  int members = max(1, min(widest, target / plan.blocks));
+  int members = max(1, min(min(widest, kMaxMembers), target / plan.blocks));
   while (members > 1 && k_blocks / members < 3) --members;  // every block keeps a few stages to stream
   plan.members = members;
   const size_t x_stride = (static_cast<size_t>(tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);

@@ -98,10 +98,13 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
     # 16 rows the mma.sync kernel wins on small matrices, whose time is all launch and ramp
     # (3.0 vs 5.1 us for the 6 MB q/k/v product), and the tcgen05 kernel on large ones (down
     # 11.4 vs 14.1 us, output head 74 vs 107 us; vendor library 16.8 and 78 us). With more
-    # rows the vendor library's tiles are a little faster than either (64 rows: down 13.3 vs
-    # 14.7 us, output head 84 vs 89 us), so it keeps those.
+    # rows the vendor library's tiles are faster on products with a short inner dimension
+    # (64 rows, q/k/v: 4.6 vs 7.7 us; output head 84 vs 89 us), and it keeps those; products with
+    # a long one (down: K = 8960 or 18944), which the tcgen05 kernel splits over a cluster,
+    # stay here up to 64 rows (32 rows 10.2 vs 13.1 us, 64 rows 11.8 vs 13.2 us; at 128 rows
+    # 15.5 vs 13.3 us the library wins again).
     if m > 16:
-        return None
+        return "stream" if stream and m <= 64 and k >= 4096 else None
     weight_bytes = 2 * n * k
     if skinny and weight_bytes < (16 << 20):
         return "skinny"
