@@ -27,6 +27,7 @@ namespace {
 constexpr int kTileKeys = 64;
 constexpr int kWarps = 4;
 constexpr int kFlashThreads = kWarps * 32;
+constexpr int kMaxClusterSplits = 16;  // splits that may merge on chip: the widest cluster
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct FlashParams {
@@ -458,15 +459,27 @@ paged_flash_attention_kernel(const FlashParams p) {
   {
     // Weights of the splits per row, gathered once: weight[r][row] = 2^(m_r - M) / L.
     float* weight = merge_o;  // [splits][16]; the warps' partials are no longer needed
-    for (int item = threadIdx.x; item < p.splits * 16; item += kFlashThreads) {
+    // Loads from the other blocks' shared memory are requested together and used afterwards:
+    // one round trip through the cluster, not one per value.
+    constexpr int kItems = (kMaxClusterSplits * 16 + kFlashThreads - 1) / kFlashThreads;
+    float2 gathered[kItems];
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int item = threadIdx.x + i * kFlashThreads;
       const int r = item >> 4, row = item & 15;
-      float2 ml = make_float2(-INFINITY, 0.f);
-      if (row < rows_total) {
-        ml.x = load_peer_f32(block_ml + row * 2, r);
-        ml.y = load_peer_f32(block_ml + row * 2 + 1, r);
+      gathered[i] = make_float2(-INFINITY, 0.f);
+      if (item < p.splits * 16 && row < rows_total) {
+        gathered[i].x = load_peer_f32(block_ml + row * 2, r);
+        gathered[i].y = load_peer_f32(block_ml + row * 2 + 1, r);
       }
-      weight[item] = ml.x;
-      weight[p.splits * 16 + item] = ml.y;
+    }
+#pragma unroll
+    for (int i = 0; i < kItems; ++i) {
+      const int item = threadIdx.x + i * kFlashThreads;
+      if (item < p.splits * 16) {
+        weight[item] = gathered[i].x;
+        weight[p.splits * 16 + item] = gathered[i].y;
+      }
     }
     __syncthreads();
     if (threadIdx.x < 16) {
@@ -485,9 +498,14 @@ paged_flash_attention_kernel(const FlashParams p) {
     const int width = max(0, d_end - d_begin);
     for (int item = threadIdx.x; item < rows_total * width; item += kFlashThreads) {
       const int row = item / width, d = d_begin + (item - row * width);
+      float values[kMaxClusterSplits];
+#pragma unroll
+      for (int r = 0; r < kMaxClusterSplits; ++r)
+        if (r < p.splits) values[r] = load_peer_f32(block_o + row * HEAD_DIM + d, r);
       float acc = 0.f;
-#pragma unroll 8
-      for (int r = 0; r < p.splits; ++r) acc += load_peer_f32(block_o + row * HEAD_DIM + d, r) * weight[r * 16 + row];
+#pragma unroll
+      for (int r = 0; r < kMaxClusterSplits; ++r)
+        if (r < p.splits) acc += values[r] * weight[r * 16 + row];
       const int tok = row / p.group;
       const int head = kv_head * p.group + (row - tok * p.group);
       const int64_t out_row = static_cast<int64_t>(q_start + tok) * p.q_heads + head;
