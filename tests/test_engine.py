@@ -252,3 +252,35 @@ def test_sampled_tokens_do_not_depend_on_running_ahead(tiny):
         assert engine.stats()["steps_ahead_used"] > 10
     with engine_for(name, folder, run_ahead=False) as engine:
         assert run_all(engine, prompts, 30, **options) == ahead
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_workloads_are_the_same_with_and_without_running_ahead(tiny, seed):
+    """Requests of random lengths arrive, stop on tokens, hit their limits and are cancelled at
+    random steps; every request's tokens must not depend on whether steps are launched ahead."""
+    name, folder, config, _ = tiny
+    vocab = config["vocab_size"]
+
+    def scenario(run_ahead: bool):
+        rng = np.random.default_rng(100 + seed)
+        with engine_for(name, folder, run_ahead=run_ahead, kv_cache_bytes=1 << 20) as engine:
+            ids = []
+            for step in range(160):
+                if step < 90 and rng.random() < 0.18:
+                    prompt = random_tokens(rng, vocab, int(rng.integers(1, 30)))
+                    stops = [int(t) for t in rng.integers(0, vocab, int(rng.integers(0, 4)))]
+                    ids.append(engine.submit(prompt, int(rng.integers(1, 40)), stops))
+                if ids and rng.random() < 0.04:
+                    engine.cancel(ids[int(rng.integers(0, len(ids)))])
+                engine.step()
+            while engine.has_work():
+                engine.step()
+            outputs = [(engine.request(r).state, list(engine.request(r).output)) for r in ids]
+            stats = engine.stats()
+            assert drained(engine)
+        return outputs, stats
+
+    ahead, stats = scenario(True)
+    behind, _ = scenario(False)
+    assert ahead == behind
+    assert stats["steps_ahead_used"] > 0 and stats["steps_ahead_dropped"] > 0
