@@ -4,7 +4,8 @@
 // head of the group) combination, as in attention_flash.cu - and walks the request's keys 128
 // at a time:
 //   S = Q K^T      tcgen05.mma, both operands in shared memory (128-byte swizzle), S in TMEM
-//   P = softmax    four warps, one thread per row: tcgen05.ld S, running max / sum in 32-bit
+//   P = softmax    two groups of four warps, one thread per row, the groups taking the key
+//                  tiles in turn: tcgen05.ld S, running max / sum in 32-bit
 //                  (python/instinct/backends/portable.py:173-188), P back to TMEM as bfloat16
 //   O += P V       tcgen05.mma with P read from TMEM and V from shared memory, O in TMEM
 // Keys and values come straight from the arena's pages: one thread walks the block table and
@@ -29,7 +30,8 @@ constexpr int kRows = 128;       // query rows per block (MMA M)
 constexpr int kKeys = 128;       // keys per tile (MMA N of S, K of PV)
 constexpr int kStagesK = 3;      // key tiles in flight: a slot is free once its S product retired
 constexpr int kStagesV = 2;      // value tiles in flight: a slot is free once its PV product retired
-constexpr int kThreadsA = 224;   // warp 0: K loads, warp 1: MMA, warps 2-5: softmax, warp 6: V loads
+constexpr int kThreadsA = 352;   // warp 0: K loads, warp 1: MMA, warps 2-5 and 6-9: softmax, warp 10: V loads
+constexpr int kSoftmaxThreads = 256;
 constexpr int kHalfBytes = kKeys * 128;  // one 64-column half of a 128-row tile: 16 KB
 constexpr int kTileBytesA = 2 * kHalfBytes;
 constexpr int kMaxChunks = 1024;  // page pieces a block may walk (block-table entries cached in smem)
@@ -170,12 +172,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t chosen;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+  return chosen != 0;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kThreadsA)
+__global__ void __launch_bounds__(kThreadsA, 1)
 flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                              const PrefillParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -185,7 +193,15 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   unsigned char* v_ring = k_ring + kStagesK * kTileBytesA;        // kStagesV x 32 KB
   int* pages = reinterpret_cast<int*>(v_ring + kStagesV * kTileBytesA);  // [kMaxChunks]
   __shared__ __align__(8) uint64_t k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
-  __shared__ __align__(8) uint64_t s_full[2], p_ready[2], o_done;
+  // o_done[t & 3] completes when PV[t] has retired (and with it every earlier product). A ring of
+  // four, because its waiters are not in step with it: a phase bit tells "done" from "not yet"
+  // only while the barrier is less than two phases from the one asked for, and every softmax
+  // thread checks PV[t - 2] at each of its tiles, which keeps all its questions within that.
+  __shared__ __align__(8) uint64_t s_full[2], p_ready[2], o_done[4];
+  // What a row's two softmax threads (one per group) tell each other: the exponent offset after
+  // the last tile decided, which tile is next to decide, and at the end their sums.
+  __shared__ float row_m[kRows], row_l[2][kRows];
+  __shared__ int row_next[kRows];
   __shared__ uint32_t tmem_base_shared;
 
   wait_for_predecessor();
@@ -224,7 +240,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     bar_init(&s_full[1], 1);
     bar_init(&p_ready[0], 128);
     bar_init(&p_ready[1], 128);
-    bar_init(&o_done, 1);
+    for (int i = 0; i < 4; ++i) bar_init(&o_done[i], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -239,6 +255,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     // Pieces past the request's last key are read too (the table pads them with a page that
     // exists): their scores are masked, and their values only ever meet a probability of zero.
     pages[i] = (key >> p.page_shift) < p.max_pages ? table[key >> p.page_shift] : -1;
+  }
+  for (int i = threadIdx.x; i < kRows; i += kThreadsA) {
+    row_m[i] = -INFINITY;
+    row_next[i] = 0;
   }
   for (int i = threadIdx.x; i < kRows * 16; i += kThreadsA) {
     const int r = i >> 4, c = i & 15;
@@ -265,9 +285,12 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const uint32_t tmem = tmem_base_shared;
   const uint32_t tmem_s[2] = {tmem, tmem + 128};
   const uint32_t tmem_o = tmem + 256;
+  // Probabilities (two bfloat16 per column) have columns of their own: the scores of tile it + 2
+  // can then be computed into the buffer tile it's scores came from while PV[it] still reads P[it].
+  const uint32_t tmem_p[2] = {tmem + 384, tmem + 448};
 
-  if ((warp == 0 || warp == 6) && lane == 0) {
-    // ---- loaders: one TMA box per page piece and 64-column half; warp 0 keys, warp 6 values ----
+  if ((warp == 0 || warp == 10) && lane == 0) {
+    // ---- loaders: one TMA box per page piece and 64-column half; warp 0 keys, warp 10 values ---
     const bool keys = warp == 0;
     const int stages = keys ? kStagesK : kStagesV;
     uint64_t* full = keys ? k_full : v_full;
@@ -300,24 +323,41 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         tma_tile(ring + s * kTileBytesA + kHalfBytes + offset, map, &full[s], 64, arena_row);
       }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---- tensor-core issuer -----------------------------------------------------------------------
+    // One thread issues every product, so the instructions between two tcgen05.mma are on the
+    // critical path (with a descriptor built from an address each time they cost about 110
+    // cycles per product, twice what the tensor core needs for it): the descriptors of the
+    // query tile and of the first ring slots are built once, and a product's descriptor is
+    // that plus a constant. The address field is 14 bits of 16-byte units and the whole of
+    // shared memory fits it, so the additions never carry out of the field.
+    // The whole warp walks the loop, so that everything the products take (descriptors,
+    // addresses) is uniform across the warp and can live in uniform registers; one elected lane
+    // issues. Inside a single-lane branch every operand had to be moved over first.
+    const bool leader = elect_one();
     const uint32_t id_s = idesc(false), id_o = idesc(true);
-    const uint32_t q_addr = saddr(q_tile);
+    const uint64_t q_desc = desc_k_major(saddr(q_tile));
+    const uint64_t k_desc = desc_k_major(saddr(k_ring));
+    const uint64_t v_desc = desc_mn_major(saddr(v_ring));
     auto scores = [&](int it) -> bool {  // S[it % 2] = Q K^T for tile `it`
       const int s = it % kStagesK;
       if (!bar_wait(&k_full[s], (it / kStagesK) & 1)) {
         return false;
       }
       fence_after();
-      const uint32_t k_addr = saddr(k_ring + s * kTileBytesA);
+      const uint64_t k_here = k_desc + static_cast<uint64_t>(s * (kTileBytesA >> 4));
+      const uint32_t d = tmem_s[it & 1];
 #pragma unroll
       for (int ks = 0; ks < kDim / 16; ++ks) {
-        const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-        mma_ss(tmem_s[it & 1], desc_k_major(q_addr + off), desc_k_major(k_addr + off), id_s, ks > 0);
+        constexpr int kHalf16 = kHalfBytes >> 4;
+        const uint64_t off = static_cast<uint64_t>((ks >> 2) * kHalf16 + (ks & 3) * 2);  // 32 bytes per 16 dims
+        if (leader) mma_ss(d, q_desc + off, k_here + off, id_s, ks > 0);
       }
-      mma_commit(&k_empty[s]);  // K[it] is no longer read
-      mma_commit(&s_full[it & 1]);
+      if (leader) {
+        mma_commit(&k_empty[s]);  // K[it] is no longer read
+        mma_commit(&s_full[it & 1]);
+      }
+      __syncwarp();
       return true;
     };
     bool ok = scores(0);
@@ -325,38 +365,64 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     for (int it = 0; it < num_tiles && ok; ++it) {
       const int s = it % kStagesV;
       // O += P V once the softmax warps have written P[it] and V[it] has landed.
-      if (!bar_wait(&p_ready[it & 1], (it >> 1) & 1) || !bar_wait(&v_full[s], (it / kStagesV) & 1)) {
+      if (!bar_wait(&p_ready[it & 1], (it >> 1) & 1)) {
+        ok = false;
+        break;
+      }
+      // The softmax group that just finished waits for its next scores: they go first.
+      if (it + 2 < num_tiles && !scores(it + 2)) {
+        ok = false;
+        break;
+      }
+      if (!bar_wait(&v_full[s], (it / kStagesV) & 1)) {
         ok = false;
         break;
       }
       fence_after();
-      const uint32_t v_addr = saddr(v_ring + s * kTileBytesA);
+      const uint64_t v_here = v_desc + static_cast<uint64_t>(s * (kTileBytesA >> 4));
+      const uint32_t p_addr = tmem_p[it & 1];
 #pragma unroll
-      for (int ks = 0; ks < kKeys / 16; ++ks)
-        mma_ts(tmem_o, tmem_s[it & 1] + ks * 8, desc_mn_major(v_addr + ks * 2048), id_o, it > 0 || ks > 0);
-      mma_commit(&v_empty[s]);  // V[it] is no longer read
-      mma_commit(&o_done);       // O holds tiles 0..it
-      if (it + 2 < num_tiles) ok = scores(it + 2);  // reuses the S buffer P[it] lived in, after PV[it]
+      for (int ks = 0; ks < kKeys / 16; ++ks)  // 16 keys: 8 columns of P, 2,048 bytes of V
+        if (leader) mma_ts(tmem_o, p_addr + ks * 8, v_here + static_cast<uint64_t>(ks * (2048 >> 4)), id_o, it > 0 || ks > 0);
+      if (leader) {
+        mma_commit(&v_empty[s]);      // V[it] is no longer read
+        mma_commit(&o_done[it & 3]);  // nor P[it]; O holds tiles 0..it
+      }
+      __syncwarp();
     }
-    if (!ok) {
+    if (!ok && leader) {
       atomicOr(p.err, ERRBIT_TIMEOUT_A);
     }
-  } else if (warp >= 2 && warp < 6) {
-    // ---- softmax: one thread per query row --------------------------------------------------------
-    const int quarter = warp & 3;
+  } else if (warp >= 2 && warp < 10) {
+    // ---- softmax: one thread per query row and group; group 0 takes the even tiles, group 1 the odd
+    // A tile's exponentials keep a quarter of the SM's special-function units busy for 1,024
+    // cycles, its maximum pass and the waits take as long again: with two groups of warps one
+    // group's maximum pass hides behind the other's exponentials. The two threads of a row
+    // (same TMEM lane, warps w and w + 4) share the row's offset m through shared memory: a
+    // tile's maximum is computed freely, but deciding whether it moves m waits until every
+    // earlier tile has decided (row_next), so m changes as if one thread walked the tiles.
+    const int quarter = warp & 3, group = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;  // row of the block = TMEM lane
     const int row = row_base + r;
     const bool live = row < rows_total;
     const int tok = min(row / p.group, q_len - 1);
     const int pos = first_pos + tok;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int it = 0; it < num_tiles; ++it) {
-      if (!__all_sync(0xffffffffu, bar_wait(&s_full[it & 1], (it >> 1) & 1))) {  // the warp leaves together
-        ok = false;
-        break;
+    volatile int* next_tile = &row_next[r];
+    volatile float* shared_m = &row_m[r];
+    float l = 0.f;            // this thread's sum, relative to the offset `seen`
+    float seen = -INFINITY;
+    bool ok = true;           // false after a wait gave up: later waits are skipped, the block runs out
+    auto turn_of = [&](int tile) -> bool {  // spins until every tile before `tile` has decided
+      if (!ok) return false;
+      const long long start = clock64();
+      while (*next_tile != tile) {
+        if (clock64() - start > kWaitCyclesA) return false;
       }
+      return true;
+    };
+    for (int it = group; it < num_tiles; it += 2) {
+      if (ok && !__all_sync(0xffffffffu, bar_wait(&s_full[it & 1], (it >> 1) & 1))) ok = false;
       fence_after();
       const int tile_start = (tile_begin + it) * kKeys;
       const uint32_t s_addr = tmem_s[it & 1] + lane_addr;
@@ -365,12 +431,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       const int rel_lo = p.window > 0 ? pos - p.window + 1 - tile_start : 0;
       const bool needs_mask = __any_sync(0xffffffffu, rel_hi < kKeys - 1 || rel_lo > 0);
       // Two passes over the scores, 32 columns at a time (rolled loops: fully unrolled, this code
-      // outgrew the instruction cache and the warps starved on fetches). Pass 1: the tile's
-      // maximum. The exponent offset `m` is only moved when that maximum exceeds it by more
-      // than kSlack (in log2 units): probabilities may then be as large as 2^kSlack, which
-      // bfloat16 and the 32-bit sums take easily, and in exchange most tiles need no rescaling
-      // of the running output, so this tile's softmax overlaps the previous tile's PV product.
-      constexpr float kSlack = 8.f;
+      // outgrew the instruction cache and the warps starved on fetches). Pass 1: the maximum.
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < kKeys; c0 += 32) {
@@ -390,33 +451,47 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
       }
       const float tile_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
+      // The offset m is only moved when this tile's maximum exceeds it by more than kSlack (in
+      // log2 units): probabilities may then be as large as 2^kSlack, which bfloat16 and the
+      // 32-bit sums take easily, and in exchange most tiles need no rescaling of the running
+      // output, so a tile's softmax overlaps the previous tile's PV product.
+      constexpr float kSlack = 8.f;
+      if (!turn_of(it)) ok = false;
+      float m = *shared_m;
+      if (m != seen) {  // the other group moved the offset since this thread's last tile
+        l *= seen == -INFINITY ? 0.f : exp2f(seen - m);
+        seen = m;
+      }
       float alpha = 1.f;
       const bool move = tile_max > m + kSlack;  // also the first finite maximum after m = -inf
-      if (__any_sync(0xffffffffu, move)) {
-        if (move) {
-          alpha = exp2f(m - tile_max);
-          m = tile_max;
-        }
-        if (it > 0) {
-          // The running output must be at rest to be rescaled: every earlier PV product retired.
-          if (!__all_sync(0xffffffffu, bar_wait(&o_done, (it - 1) & 1))) {
-            ok = false;
-            break;
-          }
-          fence_after();
-#pragma unroll 1
-          for (int c0 = 0; c0 < kDim; c0 += 32) {
-            uint32_t raw[32];
-            tmem_ld32(tmem_o + lane_addr + c0, raw);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
-            tmem_st32(tmem_o + lane_addr + c0, raw);
-          }
-          tmem_st_wait();
-        }
+      if (move) {
+        alpha = exp2f(m - tile_max);
+        m = tile_max;
+        seen = m;
+        l *= alpha;
+        *shared_m = m;
       }
-      // Pass 2: P = 2^(s * scale - m) as bfloat16 pairs, written over the front of the S buffer
-      // (columns c0/2.. of P replace scores that this thread has already read).
+      __threadfence_block();
+      *next_tile = it + 1;  // the next tile may decide; if it moves m too, it first waits for this tile's PV
+      __syncwarp();
+      if (__any_sync(0xffffffffu, move) && it > 0) {
+        // The running output must be at rest to be rescaled: every earlier PV product retired.
+        if (ok && !__all_sync(0xffffffffu, bar_wait(&o_done[(it - 1) & 3], ((it - 1) >> 2) & 1))) ok = false;
+        fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < kDim; c0 += 32) {
+          uint32_t raw[32];
+          tmem_ld32(tmem_o + lane_addr + c0, raw);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+          tmem_st32(tmem_o + lane_addr + c0, raw);
+        }
+        tmem_st_wait();
+      }
+      // Pass 2: P = 2^(s * scale - m) as bfloat16 pairs into this buffer's P columns, once the
+      // product that read them two tiles ago has retired.
+      if (it >= 2 && ok && !__all_sync(0xffffffffu, bar_wait(&o_done[(it - 2) & 3], ((it - 2) >> 2) & 1))) ok = false;
+      fence_after();
       const float offset = m == -INFINITY ? 0.f : m;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll 1
@@ -442,21 +517,28 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
           packed[i >> 1] = pack2(p0, p1);
           packed[(i >> 1) + 1] = pack2(p2, p3);
         }
-        tmem_st16(s_addr + (c0 >> 1), packed);
+        tmem_st16(tmem_p[it & 1] + lane_addr + (c0 >> 1), packed);
       }
       tmem_st_wait();
-      const float sum = (sum0 + sum1) + (sum2 + sum3);
-      l = l * alpha + sum;
+      l += (sum0 + sum1) + (sum2 + sum3);
       fence_before();
       bar_arrive(&p_ready[it & 1]);
     }
-    // The finished row: O / l, as bfloat16.
-    if (ok && num_tiles > 0) ok = bar_wait(&o_done, (num_tiles - 1) & 1);
+    // The finished row: O / l as bfloat16, l being both groups' sums brought to the final offset.
+    if (!turn_of(num_tiles)) ok = false;
+    {
+      const float m = *shared_m;
+      if (m != seen) l *= seen == -INFINITY ? 0.f : exp2f(seen - m);
+    }
+    row_l[group][r] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    l = row_l[0][r] + row_l[1][r];
+    if (ok && num_tiles > 0) ok = bar_wait(&o_done[(num_tiles - 1) & 3], ((num_tiles - 1) >> 2) & 1);
     if (!ok && lane == 0) atomicOr(p.err, ERRBIT_TIMEOUT_A);
     fence_after();
     // Every lane takes part in the warp-wide TMEM loads (they are .sync.aligned); only lanes
-    // whose row exists store. `ok` is the same for the whole warp only if no wait gave up, so
-    // after a timeout the loads are skipped by all lanes together.
+    // whose row exists store. After a timeout the loads are skipped by all lanes together.
+    // Group 0 stores the first half of the head's dims, group 1 the second.
     const bool all_ok = __all_sync(0xffffffffu, ok);
     if (all_ok) {
       const int token = min(row / p.group, q_len - 1);
@@ -464,7 +546,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       __nv_bfloat16* dst = p.out + (static_cast<int64_t>(q_start + token) * p.q_heads + head) * kDim;
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kDim; c0 += 32) {
+      for (int c0 = group * (kDim / 2); c0 < (group + 1) * (kDim / 2); c0 += 32) {
         uint32_t raw[32];
         tmem_ld32(tmem_o + lane_addr + c0, raw);
         if (live) {
