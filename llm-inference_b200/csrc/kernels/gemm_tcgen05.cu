@@ -211,27 +211,38 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       tma_load_2d(tiles + s * stage_bytes, &w_map, &full_bar[s], (kb_begin + i) * kBlockK, n0);
       tma_load_2d(tiles + s * stage_bytes + w_bytes, &x_map, &full_bar[s], (kb_begin + i) * kBlockK, 0);
     }
-  } else if (warp == 1 && lane == 0) {
+  } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------------
+    // The whole warp walks the loop and one elected lane issues: what the products take
+    // (descriptors, addresses) is then uniform across a converged warp and can stay in uniform
+    // registers, where inside a single-lane branch every operand had to be moved over for
+    // every product. A stage's descriptors are the first stage's plus a constant: the address
+    // field counts 16-byte units and all of shared memory fits it, so nothing carries out.
+    uint32_t chosen;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+    const bool leader = chosen != 0;
     const uint32_t idesc = umma_instr_desc(p.tokens_pad);
-    for (int i = 0; i < num_kb; ++i) {
+    const uint64_t a_first = umma_smem_desc(smem_addr(tiles));
+    const uint64_t b_first = umma_smem_desc(smem_addr(tiles) + w_bytes);
+    bool alive = true;
+    for (int i = 0; i < num_kb && alive; ++i) {
       const int s = i % stages;
       if (!mbar_wait(&full_bar[s], (i / stages) & 1)) {
-        atomicOr(p.err, ERRBIT_TIMEOUT);
+        if (leader) atomicOr(p.err, ERRBIT_TIMEOUT);
+        alive = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_addr = smem_addr(tiles + s * stage_bytes);
-      const uint32_t b_addr = a_addr + w_bytes;
+      const uint64_t stage_units = static_cast<uint64_t>(s) * (stage_bytes >> 4);
 #pragma unroll
       for (int k = 0; k < kBlockK / kMmaK; ++k) {
-        const uint64_t a_desc = umma_smem_desc(a_addr + k * kMmaK * 2);
-        const uint64_t b_desc = umma_smem_desc(b_addr + k * kMmaK * 2);
-        umma_bf16(tmem_base, a_desc, b_desc, idesc, i > 0 || k > 0);
+        const uint64_t step = stage_units + static_cast<uint64_t>(k * (kMmaK * 2 >> 4));
+        if (leader) umma_bf16(tmem_base, a_first + step, b_first + step, idesc, i > 0 || k > 0);
       }
-      umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+      if (leader) umma_commit(&empty_bar[s]);  // the stage may be refilled once these MMAs have read it
+      __syncwarp();
     }
-    umma_commit(&accum_bar);  // the accumulator is complete once every MMA has retired
+    if (leader) umma_commit(&accum_bar);  // the accumulator is complete once every MMA has retired
   }
   __syncwarp();
 
