@@ -11,13 +11,14 @@
 // Keys and values come straight from the arena's pages: one thread walks the block table and
 // issues TMA tile loads (cp.async.bulk.tensor) of whole page pieces into rings (three key tiles,
 // two value tiles, each with a loader thread of its own, so that a tile is on its way long
-// before its product is issued), and no thread computes addresses row by row. Two S buffers let the tensor core compute the next
-// tile's scores while the softmax warps work on the current one. Masking follows
+// before its product is issued), and no thread computes addresses row by row. Three S buffers
+// let the tensor core run two tiles ahead of each softmax group. Masking follows
 // python/instinct/batches.py:110-113: key <= query position and, with a window,
 // key > position - window.
 //
-// Every mbarrier wait is bounded; on a timeout the block records ERRBIT_TIMEOUT, stops and
-// frees its TMEM. Shapes the kernel does not take (other head sizes, pages under 16 rows,
+// Every wait (mbarriers, and the shared-memory word the two softmax threads of a row pass the
+// turn with) is bounded; on a timeout the block records ERRBIT_TIMEOUT, skips its further waits,
+// runs out and frees its TMEM. Shapes the kernel does not take (other head sizes, pages under 16 rows,
 // block tables beyond kMaxChunks page pieces) go to attention_flash.cu.
 #include <cuda.h>
 
@@ -32,6 +33,7 @@ constexpr int kStagesK = 3;      // key tiles in flight: a slot is free once its
 constexpr int kStagesV = 2;      // value tiles in flight: a slot is free once its PV product retired
 constexpr int kThreadsA = 352;   // warp 0: K loads, warp 1: MMA, warps 2-5 and 6-9: softmax, warp 10: V loads
 constexpr int kSoftmaxThreads = 256;
+constexpr int kScoreBuffers = 3;  // S tiles in TMEM (3 x 128 columns, plus 128 for O: all 512)
 constexpr int kHalfBytes = kKeys * 128;  // one 64-column half of a 128-row tile: 16 KB
 constexpr int kTileBytesA = 2 * kHalfBytes;
 constexpr int kMaxChunks = 1024;  // page pieces a block may walk (block-table entries cached in smem)
@@ -197,7 +199,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // four, because its waiters are not in step with it: a phase bit tells "done" from "not yet"
   // only while the barrier is less than two phases from the one asked for, and every softmax
   // thread checks PV[t - 2] at each of its tiles, which keeps all its questions within that.
-  __shared__ __align__(8) uint64_t s_full[2], p_ready[2], o_done[4];
+  __shared__ __align__(8) uint64_t s_full[kScoreBuffers], p_ready[kScoreBuffers], o_done[4];
   // What a row's two softmax threads (one per group) tell each other: the exponent offset after
   // the last tile decided, which tile is next to decide, and at the end their sums.
   __shared__ float row_m[kRows], row_l[2][kRows];
@@ -236,10 +238,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       bar_init(&v_full[s], 1);
       bar_init(&v_empty[s], 1);
     }
-    bar_init(&s_full[0], 1);
-    bar_init(&s_full[1], 1);
-    bar_init(&p_ready[0], 128);
-    bar_init(&p_ready[1], 128);
+    for (int i = 0; i < kScoreBuffers; ++i) {
+      bar_init(&s_full[i], 1);
+      bar_init(&p_ready[i], 128);
+    }
     for (int i = 0; i < 4; ++i) bar_init(&o_done[i], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -283,11 +285,11 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_base_shared;
-  const uint32_t tmem_s[2] = {tmem, tmem + 128};
-  const uint32_t tmem_o = tmem + 256;
-  // Probabilities (two bfloat16 per column) have columns of their own: the scores of tile it + 2
-  // can then be computed into the buffer tile it's scores came from while PV[it] still reads P[it].
-  const uint32_t tmem_p[2] = {tmem + 384, tmem + 448};
+  // TMEM: three score buffers of 128 columns, then the output. Tile t's scores live in buffer
+  // t % 3 and its probabilities (two bfloat16 per column) over their first 64 columns. With three
+  // buffers and two softmax groups, a group that hands in tile t finds the scores of tile t + 2
+  // computed already: their buffer was released when PV[t - 1] was issued.
+  const uint32_t tmem_o = tmem + kScoreBuffers * 128;
 
   if ((warp == 0 || warp == 10) && lane == 0) {
     // ---- loaders: one TMA box per page piece and 64-column half; warp 0 keys, warp 10 values ---
@@ -339,14 +341,14 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     const uint64_t q_desc = desc_k_major(saddr(q_tile));
     const uint64_t k_desc = desc_k_major(saddr(k_ring));
     const uint64_t v_desc = desc_mn_major(saddr(v_ring));
-    auto scores = [&](int it) -> bool {  // S[it % 2] = Q K^T for tile `it`
+    auto scores = [&](int it) -> bool {  // S[it % 3] = Q K^T for tile `it`
       const int s = it % kStagesK;
       if (!bar_wait(&k_full[s], (it / kStagesK) & 1)) {
         return false;
       }
       fence_after();
       const uint64_t k_here = k_desc + static_cast<uint64_t>(s * (kTileBytesA >> 4));
-      const uint32_t d = tmem_s[it & 1];
+      const uint32_t d = (tmem + (it % kScoreBuffers) * 128);
 #pragma unroll
       for (int ks = 0; ks < kDim / 16; ++ks) {
         constexpr int kHalf16 = kHalfBytes >> 4;
@@ -355,22 +357,17 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       }
       if (leader) {
         mma_commit(&k_empty[s]);  // K[it] is no longer read
-        mma_commit(&s_full[it & 1]);
+        mma_commit(&s_full[it % kScoreBuffers]);
       }
       __syncwarp();
       return true;
     };
-    bool ok = scores(0);
-    if (ok && num_tiles > 1) ok = scores(1);
+    bool ok = true;
+    for (int it = 0; it < kScoreBuffers && it < num_tiles && ok; ++it) ok = scores(it);
     for (int it = 0; it < num_tiles && ok; ++it) {
       const int s = it % kStagesV;
       // O += P V once the softmax warps have written P[it] and V[it] has landed.
-      if (!bar_wait(&p_ready[it & 1], (it >> 1) & 1)) {
-        ok = false;
-        break;
-      }
-      // The softmax group that just finished waits for its next scores: they go first.
-      if (it + 2 < num_tiles && !scores(it + 2)) {
+      if (!bar_wait(&p_ready[it % kScoreBuffers], (it / kScoreBuffers) & 1)) {
         ok = false;
         break;
       }
@@ -380,7 +377,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       }
       fence_after();
       const uint64_t v_here = v_desc + static_cast<uint64_t>(s * (kTileBytesA >> 4));
-      const uint32_t p_addr = tmem_p[it & 1];
+      const uint32_t p_addr = (tmem + (it % kScoreBuffers) * 128);
 #pragma unroll
       for (int ks = 0; ks < kKeys / 16; ++ks)  // 16 keys: 8 columns of P, 2,048 bytes of V
         if (leader) mma_ts(tmem_o, p_addr + ks * 8, v_here + static_cast<uint64_t>(ks * (2048 >> 4)), id_o, it > 0 || ks > 0);
@@ -389,6 +386,11 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         mma_commit(&o_done[it & 3]);  // nor P[it]; O holds tiles 0..it
       }
       __syncwarp();
+      // The buffer P[it] lives in takes the scores of tile it + 3 (products run in issue order).
+      if (it + kScoreBuffers < num_tiles && !scores(it + kScoreBuffers)) {
+        ok = false;
+        break;
+      }
     }
     if (!ok && leader) {
       atomicOr(p.err, ERRBIT_TIMEOUT_A);
@@ -422,10 +424,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
       return true;
     };
     for (int it = group; it < num_tiles; it += 2) {
-      if (ok && !__all_sync(0xffffffffu, bar_wait(&s_full[it & 1], (it >> 1) & 1))) ok = false;
+      if (ok && !__all_sync(0xffffffffu, bar_wait(&s_full[it % kScoreBuffers], (it / kScoreBuffers) & 1))) ok = false;
       fence_after();
       const int tile_start = (tile_begin + it) * kKeys;
-      const uint32_t s_addr = tmem_s[it & 1] + lane_addr;
+      const uint32_t s_addr = (tmem + (it % kScoreBuffers) * 128) + lane_addr;
       // Keys [rel_lo, rel_hi] of this tile are the ones this row attends to.
       const int rel_hi = live ? pos - tile_start : -1;
       const int rel_lo = p.window > 0 ? pos - p.window + 1 - tile_start : 0;
@@ -488,8 +490,9 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         }
         tmem_st_wait();
       }
-      // Pass 2: P = 2^(s * scale - m) as bfloat16 pairs into this buffer's P columns, once the
-      // product that read them two tiles ago has retired.
+      // Pass 2: P = 2^(s * scale - m) as bfloat16 pairs, written over the front of the S buffer
+      // (columns c0/2.. of P replace scores that this thread has already read). The look at
+      // PV[it - 2] first is what keeps this thread's view of the o_done ring current (see there).
       if (it >= 2 && ok && !__all_sync(0xffffffffu, bar_wait(&o_done[(it - 2) & 3], ((it - 2) >> 2) & 1))) ok = false;
       fence_after();
       const float offset = m == -INFINITY ? 0.f : m;
@@ -517,12 +520,12 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
           packed[i >> 1] = pack2(p0, p1);
           packed[(i >> 1) + 1] = pack2(p2, p3);
         }
-        tmem_st16(tmem_p[it & 1] + lane_addr + (c0 >> 1), packed);
+        tmem_st16((tmem + (it % kScoreBuffers) * 128) + lane_addr + (c0 >> 1), packed);
       }
       tmem_st_wait();
       l += (sum0 + sum1) + (sum2 + sum3);
       fence_before();
-      bar_arrive(&p_ready[it & 1]);
+      bar_arrive(&p_ready[it % kScoreBuffers]);
     }
     // The finished row: O / l as bfloat16, l being both groups' sums brought to the final offset.
     if (!turn_of(num_tiles)) ok = false;
