@@ -206,8 +206,6 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   __shared__ int row_next[kRows];
   __shared__ uint32_t tmem_base_shared;
 
-  wait_for_predecessor();
-  let_successor_start();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seq = p.first_seq + blockIdx.z;
   const int kv_head = blockIdx.y;
@@ -250,8 +248,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // Block-table entries of every page piece this block walks, and the query tile (swizzled by
-  // hand: chunk c of row r goes to chunk c ^ (r & 7) of its 128-byte row).
+  // Block-table entries of every page piece this block walks: like the lengths above they are
+  // part of the step's metadata, on the device before any kernel of the step ran, so all of
+  // this may precede the wait for the kernel in front (which wrote the queries and the newest
+  // keys).
   for (int i = threadIdx.x; i < num_tiles * pieces_per_tile; i += kThreadsA) {
     const int key = tile_begin * kKeys + i * p.piece_rows;
     // Pieces past the request's last key are read too (the table pads them with a page that
@@ -262,28 +262,39 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     row_m[i] = -INFINITY;
     row_next[i] = 0;
   }
-  for (int i = threadIdx.x; i < kRows * 16; i += kThreadsA) {
-    const int r = i >> 4, c = i & 15;
-    const int row = row_base + r;
-    uint4 value = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows_total) {
-      const int tok = row / p.group;
-      const int head = kv_head * p.group + (row - tok * p.group);
-      value = *reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_start + tok) * p.q_heads + head) * kDim + c * 8);
-    }
-    *reinterpret_cast<uint4*>(q_tile + (c >> 3) * kHalfBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = value;
-  }
+  wait_for_predecessor();
+  let_successor_start();
   if (p.window > 0 || tile_end * kKeys > p.max_pages * p.page_size) {
     // Pieces whose page the request no longer holds, or that lie past the block table, are
     // skipped by the loader; their rows must still hold finite numbers, since a masked
     // probability of zero times garbage may be NaN.
     for (int i = threadIdx.x; i < (kStagesK + kStagesV) * kTileBytesA / 16; i += kThreadsA)
       reinterpret_cast<uint4*>(k_ring)[i] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   fence_before();
   __syncthreads();
   fence_after();
+  // The loaders go ahead; the other nine warps bring the query tile in meanwhile (swizzled by
+  // hand: chunk c of row r goes to chunk c ^ (r & 7) of its 128-byte row) and meet the issuing
+  // warp at a barrier of their own.
+  constexpr int kFillThreads = 9 * 32;
+  if (warp >= 1 && warp <= 9) {
+    for (int i = threadIdx.x - 32; i < kRows * 16; i += kFillThreads) {
+      const int r = i >> 4, c = i & 15;
+      const int row = row_base + r;
+      uint4 value = make_uint4(0u, 0u, 0u, 0u);
+      if (row < rows_total) {
+        const int tok = row / p.group;
+        const int head = kv_head * p.group + (row - tok * p.group);
+        value = *reinterpret_cast<const uint4*>(p.q + (static_cast<int64_t>(q_start + tok) * p.q_heads + head) * kDim + c * 8);
+      }
+      *reinterpret_cast<uint4*>(q_tile + (c >> 3) * kHalfBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = value;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 1) asm volatile("bar.sync 2, %0;" ::"n"(kFillThreads) : "memory");
+    else asm volatile("bar.arrive 2, %0;" ::"n"(kFillThreads) : "memory");
+  }
   const uint32_t tmem = tmem_base_shared;
   // TMEM: three score buffers of 128 columns, then the output. Tile t's scores live in buffer
   // t % 3 and its probabilities (two bfloat16 per column) over their first 64 columns. With three
