@@ -302,8 +302,10 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   // computed already: their buffer was released when PV[t - 1] was issued.
   const uint32_t tmem_o = tmem + kScoreBuffers * 128;
 
-  if ((warp == 0 || warp == 10) && lane == 0) {
+  if (warp == 0 || warp == 10) {
     // ---- loaders: one TMA box per page piece and 64-column half; warp 0 keys, warp 10 values ---
+    // (a converged warp with one elected lane issuing, as for the products below)
+    const bool leader = elect_one();
     const bool keys = warp == 0;
     const int stages = keys ? kStagesK : kStagesV;
     uint64_t* full = keys ? k_full : v_full;
@@ -313,7 +315,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
     for (int it = 0; it < num_tiles; ++it) {
       const int s = it % stages;
       if (it >= stages && !bar_wait(&empty[s], ((it / stages) - 1) & 1)) {
-        atomicOr(p.err, ERRBIT_TIMEOUT_A);
+        if (leader) atomicOr(p.err, ERRBIT_TIMEOUT_A);
         break;
       }
       uint32_t bytes = 0;
@@ -321,20 +323,23 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
         const int page = pages[it * pieces_per_tile + piece];
         if (page >= 0 && page < p.num_pages) bytes += 2u * p.piece_rows * 128u;
       }
-      bar_expect_tx(&full[s], bytes);
+      if (leader) bar_expect_tx(&full[s], bytes);
       for (int piece = 0; piece < pieces_per_tile; ++piece) {
         const int page = pages[it * pieces_per_tile + piece];
         if (page < 0) continue;
         if (page >= p.num_pages) {
-          atomicOr(p.err, ERRBIT_BAD_PAGE);
+          if (leader) atomicOr(p.err, ERRBIT_BAD_PAGE);
           continue;
         }
         const int key = (tile_begin + it) * kKeys + piece * p.piece_rows;
         const int arena_row = (page * p.kv_heads + kv_head) * p.page_size + (key & (p.page_size - 1));
         const int offset = piece * p.piece_rows * 128;
-        tma_tile(ring + s * kTileBytesA + offset, map, &full[s], 0, arena_row);
-        tma_tile(ring + s * kTileBytesA + kHalfBytes + offset, map, &full[s], 64, arena_row);
+        if (leader) {
+          tma_tile(ring + s * kTileBytesA + offset, map, &full[s], 0, arena_row);
+          tma_tile(ring + s * kTileBytesA + kHalfBytes + offset, map, &full[s], 64, arena_row);
+        }
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
     // ---- tensor-core issuer -----------------------------------------------------------------------
