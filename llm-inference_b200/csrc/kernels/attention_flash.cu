@@ -525,6 +525,31 @@ __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
   let_successor_start();
   const int64_t row = blockIdx.x;
   const float2* ml = reinterpret_cast<const float2*>(partial_ml + row * splits * 2);
+  if (splits <= kMaxClusterSplits && HEAD_DIM <= static_cast<int>(blockDim.x)) {
+    // Every load of this thread (the splits' maxima and sums, and its dim of every split's
+    // output) is requested before the first is used: one round trip to L2 instead of three.
+    const int d = threadIdx.x;
+    float2 stats[kMaxClusterSplits];
+    float values[kMaxClusterSplits];
+#pragma unroll
+    for (int i = 0; i < kMaxClusterSplits; ++i) {
+      stats[i] = i < splits ? ml[i] : make_float2(-INFINITY, 0.f);
+      values[i] = i < splits && d < HEAD_DIM ? partial_out[(row * splits + i) * HEAD_DIM + d] : 0.f;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxClusterSplits; ++i) m = fmaxf(m, stats[i].x);
+    const float use = m == -INFINITY ? 0.f : m;
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxClusterSplits; ++i) {
+      const float f = exp2f(stats[i].x - use);
+      l += stats[i].y * f;
+      acc += values[i] * f;
+    }
+    if (d < HEAD_DIM) out[row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    return;
+  }
   float m = -INFINITY;
 #pragma unroll 8
   for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i].x);
