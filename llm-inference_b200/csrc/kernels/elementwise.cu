@@ -138,26 +138,40 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__
                                     const float* __restrict__ weight, T* __restrict__ out,
                                     const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float scratch[32];
+  // The weights are constants and the row list is part of the step's metadata: both are read
+  // before the wait for the kernel in front. After it, everything else this thread reads (its
+  // piece of the row and of the pending branch output) is requested before anything is used.
+  float4 v[kNormVecCache], d[kNormVecCache], w[kNormVecCache];
+#pragma unroll
+  for (int j = 0; j < kNormVecCache; ++j) {
+    const int i = 4 * (threadIdx.x + j * blockDim.x);
+    w[j] = i < hidden ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   wait_for_predecessor();
   let_successor_start();
-  const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* xr = x + static_cast<int64_t>(r) * hidden;
   const T* dr = delta ? delta + static_cast<int64_t>(r) * hidden : nullptr;
   T* outr = out + static_cast<int64_t>(blockIdx.x) * hidden;
-  float4 v[kNormVecCache];
+#pragma unroll
+  for (int j = 0; j < kNormVecCache; ++j) {
+    const int i = 4 * (threadIdx.x + j * blockDim.x);
+    v[j] = d[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < hidden) {
+      v[j] = *reinterpret_cast<const float4*>(xr + i);
+      if (dr) d[j] = Quad<T>::load(dr + i);
+    }
+  }
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < kNormVecCache; ++j) {
     const int i = 4 * (threadIdx.x + j * blockDim.x);
-    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < hidden) {
-      v[j] = *reinterpret_cast<const float4*>(xr + i);
       if (dr) {
-        const float4 d = Quad<T>::load(dr + i);
-        v[j].x += d.x;
-        v[j].y += d.y;
-        v[j].z += d.z;
-        v[j].w += d.w;
+        v[j].x += d[j].x;
+        v[j].y += d[j].y;
+        v[j].z += d[j].z;
+        v[j].w += d[j].w;
         if (!rows) *reinterpret_cast<float4*>(xr + i) = v[j];
       }
       ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
@@ -168,10 +182,9 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__
 #pragma unroll
   for (int j = 0; j < kNormVecCache; ++j) {
     const int i = 4 * (threadIdx.x + j * blockDim.x);
-    if (i < hidden) {
-      const float4 w = *reinterpret_cast<const float4*>(weight + i);
-      Quad<T>::store(outr + i, make_float4(v[j].x * inv * w.x, v[j].y * inv * w.y, v[j].z * inv * w.z, v[j].w * inv * w.w));
-    }
+    if (i < hidden)
+      Quad<T>::store(outr + i, make_float4(v[j].x * inv * w[j].x, v[j].y * inv * w[j].y, v[j].z * inv * w[j].z,
+                                           v[j].w * inv * w[j].w));
   }
 }
 

@@ -23,36 +23,56 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
                                      int kv_heads, int head_dim, int rot, int page_size,
                                      int write_kv, int* __restrict__ err) {
-  wait_for_predecessor();
-  let_successor_start();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0 .. q_heads + 2 * kv_heads
   const int rotated_heads = q_heads + kv_heads;
   const bool is_q = head < q_heads, is_k = !is_q && head < rotated_heads;
-  if (!is_q && !write_kv) return;
+  if (!is_q && !write_kv) {
+    wait_for_predecessor();
+    let_successor_start();
+    return;
+  }
+  // Where the row goes and by what angle it turns comes from the step's metadata and from
+  // constants, both on the device before the kernel in front ran: fetched before the wait for
+  // it, the chain position -> table entry costs nothing afterwards.
   const int pos = positions[t];
   const int half_rot = rot / 2, half = head_dim / 2;
-
-  T* dst;
+  T* dst = nullptr;
   if (is_q) {
     dst = q_out + (static_cast<int64_t>(t) * q_heads + head) * head_dim;
   } else {
     const int logical = pos / page_size;
     if (pos < 0 || logical >= max_pages) {
       if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_POSITION);
-      return;
+    } else {
+      const int page = block_table[static_cast<int64_t>(token_seq[t]) * max_pages + logical];
+      if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
+      } else {
+        const int kv_head = is_k ? head - q_heads : head - rotated_heads;
+        dst = (is_k ? k_arena : v_arena) + kv_row_offset(page, kv_head, pos % page_size, kv_heads, page_size, head_dim);
+      }
     }
-    const int page = block_table[static_cast<int64_t>(token_seq[t]) * max_pages + logical];
-    if (page < 0 || page >= num_pages) {
-      if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
-      return;
-    }
-    const int kv_head = is_k ? head - q_heads : head - rotated_heads;
-    dst = (is_k ? k_arena : v_arena) + kv_row_offset(page, kv_head, pos % page_size, kv_heads, page_size, head_dim);
   }
   const int width = (q_heads + 2 * kv_heads) * head_dim;
   const T* src = qkv + static_cast<int64_t>(t) * width + head * head_dim;
   const float* b = bias ? bias + head * head_dim : nullptr;
+  // This thread's first pair slot (the only one when the block has a thread per slot): its
+  // bias and its sine and cosine, also ahead of the wait.
+  const int first_slot = threadIdx.x;
+  float first_b0 = 0.f, first_b1 = 0.f, first_sn = 0.f, first_cs = 1.f;
+  if (first_slot < half) {
+    const int d0 = first_slot < half_rot ? first_slot : rot + 2 * (first_slot - half_rot);
+    const int d1 = first_slot < half_rot ? first_slot + half_rot : d0 + 1;
+    if (b) {
+      first_b0 = b[d0];
+      first_b1 = b[d1];
+    }
+    if ((is_q || is_k) && first_slot < half_rot) sincosf(static_cast<float>(pos) * inv_freq[first_slot], &first_sn, &first_cs);
+  }
+  wait_for_predecessor();
+  let_successor_start();
+  if (dst == nullptr) return;
 
   // Pair slot i: below rot/2 it is the rotated pair (i, i + rot/2); the rest are the two
   // trailing dims a partial rotation leaves alone. Value heads are copied (bias added).
@@ -67,13 +87,18 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
       d1 = d0 + 1;
     }
     float x0 = to_f32<T>(src[d0]), x1 = to_f32<T>(src[d1]);
-    if (b) {
-      x0 += b[d0];
-      x1 += b[d1];
+    float sn = first_sn, cs = first_cs;
+    if (slot == first_slot) {
+      x0 += first_b0;
+      x1 += first_b1;
+    } else {
+      if (b) {
+        x0 += b[d0];
+        x1 += b[d1];
+      }
+      if (rotate) sincosf(static_cast<float>(pos) * inv_freq[slot], &sn, &cs);
     }
     if (rotate) {
-      float sn, cs;
-      sincosf(static_cast<float>(pos) * inv_freq[slot], &sn, &cs);
       const float y0 = x0 * cs - x1 * sn, y1 = x1 * cs + x0 * sn;
       x0 = y0;
       x1 = y1;
