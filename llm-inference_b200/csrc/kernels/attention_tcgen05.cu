@@ -226,6 +226,12 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int tile_begin = lo / kKeys, tile_end = hi / kKeys + 1;
   const int num_tiles = tile_end - tile_begin;
   const int pieces_per_tile = kKeys / p.piece_rows;
+  if (num_tiles * pieces_per_tile > kMaxChunks) {
+    // The launcher sized the walk from the host's lengths; lengths on the device that exceed
+    // them are an error of the caller, reported rather than walked.
+    if (threadIdx.x == 0) atomicOr(p.err, ERRBIT_BAD_POSITION);
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesK; ++s) {

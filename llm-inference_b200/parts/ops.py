@@ -373,5 +373,5 @@ def argmax_rows(lib, logits: torch.Tensor, out: torch.Tensor, row_index: torch.T
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "argmax: logits must be float32 rows")
     lib.call(
         "b200_argmax_rows", ptr(logits), c_int(rows), c_int(logits.shape[1]), c_int64(logits.stride(0)),
-        ptr(row_index), ptr(out), stream,
+        ptr(row_index), ptr(out), ptr(None), ptr(None), stream,
     )

@@ -25,6 +25,9 @@ class Sampler:
         self._dev = torch.empty(max_rows * 8, dtype=torch.int32, device=device)
         self._tokens = torch.zeros(max_rows + 1, dtype=torch.int32, device=device)
         self._tokens_host = torch.zeros(max_rows + 1, dtype=torch.int32, pin_memory=True)
+        # Scratch of the arg-max over many blocks per row: zero now, left zero by every launch.
+        self._best = torch.zeros(max_rows, dtype=torch.int64, device=device)
+        self._arrived = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._done = torch.cuda.Event()  # recorded after the copy of a step's tokens to the host
 
     @property
@@ -62,7 +65,7 @@ class Sampler:
         if not sampled:
             self.lib.call(
                 "b200_argmax_rows", ptr(logits), c_int(rows), c_int(vocab), c_int64(logits.stride(0)),
-                c_void_p(0), ptr(tokens), s,
+                c_void_p(0), ptr(tokens), ptr(self._best), ptr(self._arrived), s,
             )
         else:
             n, g = len(sampled), len(greedy)
@@ -80,7 +83,7 @@ class Sampler:
             if g:
                 self.lib.call(
                     "b200_argmax_rows", ptr(logits), c_int(g), c_int(vocab), c_int64(logits.stride(0)),
-                    ptr(dev[5 * m :]), ptr(tokens), s,
+                    ptr(dev[5 * m :]), ptr(tokens), ptr(self._best), ptr(self._arrived), s,
                 )
             self.lib.call(
                 "b200_sample_rows", ptr(logits), c_int(n), c_int(vocab), c_int64(logits.stride(0)),

@@ -533,23 +533,33 @@ def test_flash_attention_finds_one_far_key_and_respects_the_window_edge(lib):
             assert abs(out[row, 0].item() - sum(visible) / len(visible)) < 0.3, (pos, out[row, 0].item())
 
 
-def test_argmax_rows_takes_the_lowest_index_on_ties(lib):
-    logits = torch.randn(6, 1511, device="cuda")
+@pytest.mark.parametrize("vocab,many_blocks", [(1511, False), (1511, True), (151936, True), (40001, True)])
+def test_argmax_rows_takes_the_lowest_index_on_ties(lib, vocab, many_blocks):
+    """One block per row, and (with scratch, from 4,096 entries on) many blocks per row."""
+    torch.manual_seed(vocab)
+    logits = torch.randn(6, vocab, device="cuda")
     logits[0, 700] = logits[0, 33] = 50.0
-    logits[1, 1510] = 60.0
+    logits[1, vocab - 1] = 60.0
     logits[2, 0] = 60.0
     logits[3] = 0.0
+    logits[5, vocab // 2 + 3] = logits[5, vocab - 2] = 70.0  # a tie across blocks
     out = torch.full((6,), -1, dtype=torch.int32, device="cuda")
+    best = torch.zeros(8, dtype=torch.int64, device="cuda")
+    arrived = torch.zeros(8, dtype=torch.int32, device="cuda")
+    scratch = (c_void_p(best.data_ptr()), c_void_p(arrived.data_ptr())) if many_blocks else (c_void_p(0), c_void_p(0))
     s = c_void_p(torch.cuda.current_stream().cuda_stream)
-    lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(6), c_int(1511), c_int64(1511), c_void_p(0), c_void_p(out.data_ptr()), s)
     want = logits.argmax(-1).tolist()
-    want[0], want[3] = 33, 0
-    assert out.tolist() == want
+    want[0], want[3], want[5] = 33, 0, vocab // 2 + 3
+    for _ in range(2):  # the scratch serves every launch
+        out.fill_(-1)
+        lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(6), c_int(vocab), c_int64(vocab), c_void_p(0), c_void_p(out.data_ptr()), *scratch, s)
+        assert out.tolist() == want
+        assert int(best.abs().sum()) == 0 and int(arrived.sum()) == 0
     # Only some rows.
     rows = torch.tensor([4, 1], dtype=torch.int32, device="cuda")
     out.fill_(-1)
-    lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(2), c_int(1511), c_int64(1511), c_void_p(rows.data_ptr()), c_void_p(out.data_ptr()), s)
-    assert out.tolist() == [-1, 1510, -1, -1, want[4], -1]
+    lib.call("b200_argmax_rows", c_void_p(logits.data_ptr()), c_int(2), c_int(vocab), c_int64(vocab), c_void_p(rows.data_ptr()), c_void_p(out.data_ptr()), *scratch, s)
+    assert out.tolist() == [-1, vocab - 1, -1, -1, want[4], -1]
 
 
 def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys):
