@@ -28,6 +28,8 @@ class Sampler:
         # Scratch of the arg-max over many blocks per row: zero now, left zero by every launch.
         self._best = torch.zeros(max_rows, dtype=torch.int64, device=device)
         self._arrived = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.lib.lib.b200_sample_scratch_bytes.restype = c_int64
+        self._sample_scratch = torch.zeros(int(self.lib.lib.b200_sample_scratch_bytes(max_rows)), dtype=torch.uint8, device=device)
         self._done = torch.cuda.Event()  # recorded after the copy of a step's tokens to the host
 
     @property
@@ -88,7 +90,7 @@ class Sampler:
             self.lib.call(
                 "b200_sample_rows", ptr(logits), c_int(n), c_int(vocab), c_int64(logits.stride(0)),
                 ptr(dev[0:]), ptr(dev[m:]), ptr(dev[2 * m :]), ptr(dev[3 * m :]), ptr(dev[6 * m :]),
-                ptr(dev[4 * m :]), ptr(tokens), s,
+                ptr(dev[4 * m :]), ptr(tokens), ptr(self._sample_scratch), c_int64(self._sample_scratch.numel()), s,
             )
         if err is not None:
             tokens[rows : rows + 1].copy_(err)

@@ -300,6 +300,19 @@ def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page, runs)
     assert int(ctx.err.item()) & 1
 
 
+def test_sampling_rows_with_too_many_equal_logits_take_the_long_way(lib):
+    """5,000 equal logits are all candidates and do not fit the list of the many-block path: the
+    row falls back to the one-block scan and must give what that gives."""
+    vocab, draws = 5000, 64
+    logits = torch.zeros(draws, vocab, device="cuda")
+    logits[:, 123] = 1.0
+    keys = [plain.draw_key(5, i) for i in range(draws)]
+    args = ([0.9] * draws, [1.0] * draws, [0.0] * draws, [0] * draws, keys)
+    one = run_sampler(lib, logits, *args, many_blocks=False)
+    many = run_sampler(lib, logits, *args, many_blocks=True)
+    assert one == many and len(set(one)) > 20
+
+
 def dense_attention(q, k, v, scale, window, start):
     """q [n, heads, d] at positions start..start+n-1 over k, v [start+n, kv_heads, d], float64."""
     n, heads, d = q.shape
@@ -562,8 +575,11 @@ def test_argmax_rows_takes_the_lowest_index_on_ties(lib, vocab, many_blocks):
     assert out.tolist() == [-1, vocab - 1, -1, -1, want[4], -1]
 
 
-def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys):
+def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys, many_blocks=False):
+    """``many_blocks``: with scratch, so that large vocabularies are scanned by many blocks a row."""
     rows, vocab = logits.shape
+    lib.lib.b200_sample_scratch_bytes.restype = c_int64
+    scratch = torch.zeros(int(lib.lib.b200_sample_scratch_bytes(rows)) if many_blocks else 16, dtype=torch.uint8, device="cuda")
     f = lambda v: torch.tensor(v, dtype=torch.float32, device="cuda")
     t, p, m = f(temperature), f(top_p), f(min_p)
     k = torch.tensor(top_k, dtype=torch.int32, device="cuda")
@@ -572,8 +588,13 @@ def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys):
     lib.call(
         "b200_sample_rows", c_void_p(logits.data_ptr()), c_int(rows), c_int(vocab), c_int64(logits.stride(0)),
         c_void_p(t.data_ptr()), c_void_p(p.data_ptr()), c_void_p(m.data_ptr()), c_void_p(k.data_ptr()),
-        c_void_p(key.data_ptr()), c_void_p(0), c_void_p(out.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream),
+        c_void_p(key.data_ptr()), c_void_p(0), c_void_p(out.data_ptr()),
+        c_void_p(scratch.data_ptr() if many_blocks else 0), c_int64(scratch.numel()), c_void_p(torch.cuda.current_stream().cuda_stream),
     )
+    if many_blocks:
+        # The histogram (256 words), and after prefix, mask and remaining the arrival counter, the
+        # cursor and the overflow flag are back at zero.
+        assert int(scratch[:1024].sum()) == 0 and int(scratch[1036:1048].sum()) == 0
     return out.tolist()
 
 
@@ -586,9 +607,12 @@ def run_sampler(lib, logits, temperature, top_p, min_p, top_k, keys):
         (311, dict(temperature=1.0, min_p=0.15)),
         (5000, dict(temperature=1.0)),  # more tokens than candidates: only the top 1024 may be drawn
         (5000, dict(temperature=0.7, top_k=40, top_p=0.9, min_p=0.02)),
+        (2000, dict(temperature=1.1, top_p=0.95)),  # with scratch: the whole row is the list
+        (50021, dict(temperature=0.9, top_k=300, top_p=0.92, min_p=0.001)),
     ],
 )
-def test_sampling_matches_the_plain_filters_and_draw(lib, vocab, settings):
+@pytest.mark.parametrize("many_blocks", [False, True], ids=["one_block", "many_blocks"])
+def test_sampling_matches_the_plain_filters_and_draw(lib, vocab, settings, many_blocks):
     rng = np.random.default_rng(vocab)
     base = torch.from_numpy(rng.normal(0, 2.0, vocab).astype(np.float32)).cuda()
     draws = 400
@@ -596,7 +620,7 @@ def test_sampling_matches_the_plain_filters_and_draw(lib, vocab, settings):
     keys = [plain.draw_key(99, i) for i in range(draws)]
     temperature = settings.get("temperature", 1.0)
     top_k, top_p, min_p = settings.get("top_k", 0), settings.get("top_p", 1.0), settings.get("min_p", 0.0)
-    got = run_sampler(lib, logits, [temperature] * draws, [top_p] * draws, [min_p] * draws, [top_k] * draws, keys)
+    got = run_sampler(lib, logits, [temperature] * draws, [top_p] * draws, [min_p] * draws, [top_k] * draws, keys, many_blocks)
     probs = plain.surviving_probabilities(base.cpu().numpy(), temperature, top_k, top_p, min_p)
     assert all(probs[t] > 0 for t in got), "a filtered token was drawn"
     # The engine draws by inverse CDF in token order with u = uniform_from_key(key).
@@ -608,5 +632,5 @@ def test_sampling_matches_the_plain_filters_and_draw(lib, vocab, settings):
         agree += token == expected
     assert agree >= draws - 2, f"only {agree} of {draws} draws match the plain inverse CDF"
     # Same key, same token; and the result does not depend on the row it sits in.
-    again = run_sampler(lib, logits[:3], [temperature] * 3, [top_p] * 3, [min_p] * 3, [top_k] * 3, [keys[7], keys[7], keys[0]])
+    again = run_sampler(lib, logits[:3], [temperature] * 3, [top_p] * 3, [min_p] * 3, [top_k] * 3, [keys[7], keys[7], keys[0]], many_blocks)
     assert again[0] == again[1] == got[7] and again[2] == got[0]
