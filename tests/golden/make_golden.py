@@ -1,6 +1,6 @@
 """Runs the reference's own Qwen2 model code on the CPU and records its outputs.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference PATH_TO_THE_REFERENCE_CHECKOUT
 
 The reference's tested engine (python/instinct/mlx_engine.py + backends/dense.py + batches.py +
 paged_kv.py) is written against MLX, which exists only for Apple hardware. Its model code is
@@ -192,7 +192,7 @@ def compare_with_plain(case: dict, tensors: dict[str, np.ndarray], reference: di
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--reference", default="/root/reference", help="checkout of KavinP21/LLM-Inference")
+    parser.add_argument("--reference", required=True, help="checkout of KavinP21/LLM-Inference")
     args = parser.parse_args()
     install_stand_in()
     sys.path.insert(0, str(Path(args.reference) / "python"))
