@@ -1,5 +1,7 @@
-"""Each part alone against the plain implementation, and a toy mixer with state of its own
-that is registered, built and stepped without touching the framework."""
+"""Each part alone against the plain implementation, and toy architectures defined here only:
+a mixer with state of its own; another position encoding, a routed feed-forward in some layers
+and a layer that runs twice. Each is registered, built and stepped without touching the
+framework."""
 
 from __future__ import annotations
 
@@ -244,3 +246,172 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                 tokens.append(out[-1])
             assert engine.request(rid).output == out
         assert engine.stats()["free_state_slots"] == 3
+
+
+def register_routed_toy():
+    """A second toy architecture, defined here only: the stock attention mixer with another
+    position encoding (rotary angles of position / 4, as position interpolation does), a routed
+    feed-forward (two experts, the better one per token by a 32-bit router) in the odd layers and
+    the stock SwiGLU in the even ones, and a run order that visits layer 0 twice."""
+    from dataclasses import dataclass
+
+    from llm_inference_b200.config import ModelConfig, register_architecture
+    from llm_inference_b200.parts.base import Part, PartSpec, register_part
+    from llm_inference_b200.parts.model import LayerCall, ModelRecipe
+    from llm_inference_b200.weights.loader import TensorSpec
+
+    class SquashedRotary(Part):
+        """Rotary encoding at ``position / factor``: all the mixer asks of a position part is
+        the table of inverse frequencies it multiplies positions with."""
+
+        def __init__(self, *, head_dim: int, theta: float, factor: float) -> None:
+            self.head_dim, self.theta, self.factor = head_dim, float(theta), float(factor)
+            self.inv_freq = None
+
+        def load(self, tensors, dtype, device):
+            table = plain.rope_inverse_frequencies(self.head_dim, self.theta) / np.float32(self.factor)
+            self.inv_freq = torch.from_numpy(table.astype(np.float32)).to(device)
+
+    class TwoExperts(Part):
+        """``out = p * expert_e(h)`` with ``e = argmax(router(h))`` and ``p`` its softmax
+        probability, the router in 32-bit; each expert is down(silu(gate h) * up h)."""
+
+        graph_safe = False
+
+        def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int) -> None:
+            self.prefix, self.hidden_size, self.intermediate_size = prefix, hidden_size, intermediate_size
+
+        def tensor_specs(self):
+            p, h, i = self.prefix, self.hidden_size, self.intermediate_size
+            specs = [TensorSpec(p + "router.weight", (2, h))]
+            for e in range(2):
+                specs += [TensorSpec(f"{p}experts.{e}.gate.weight", (i, h)), TensorSpec(f"{p}experts.{e}.up.weight", (i, h)),
+                          TensorSpec(f"{p}experts.{e}.down.weight", (h, i))]
+            return specs
+
+        def load(self, tensors, dtype, device):
+            self.router = tensors[self.prefix + "router.weight"].to(device=device, dtype=torch.float32)
+            self.experts = [
+                tuple(tensors[f"{self.prefix}experts.{e}.{n}.weight"].to(device=device, dtype=dtype) for n in ("gate", "up", "down"))
+                for e in range(2)
+            ]
+
+        def weight_bytes(self):
+            return sum(t.numel() * t.element_size() for expert in self.experts for t in expert) + self.router.numel() * 4
+
+        def forward(self, ctx, h):
+            probs = torch.softmax(h.float() @ self.router.t(), dim=-1)
+            choice = probs.argmax(dim=-1)
+            out = torch.zeros_like(h)
+            for e, (gate, up, down) in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows]
+                    y = (torch.nn.functional.silu(x @ gate.t()) * (x @ up.t())) @ down.t()
+                    out[rows] = (y.float() * probs[rows, e : e + 1]).to(h.dtype)
+            return out
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        intermediate_size: int = 0
+        heads: int = 0
+        kv_heads: int = 0
+        head_dim: int = 0
+        theta: float = 10000.0
+        eps: float = 1e-6
+
+        @classmethod
+        def from_json_dict(cls, raw):
+            return cls("ToyRoutedForCausalLM", raw["vocab_size"], raw["hidden_size"], raw["num_hidden_layers"],
+                       raw["max_position_embeddings"], (), raw["intermediate_size"], raw["heads"], raw["kv_heads"],
+                       raw["head_dim"], raw["theta"], raw["eps"])
+
+        def to_json_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                        num_hidden_layers=self.num_hidden_layers, max_position_embeddings=self.max_position_embeddings,
+                        intermediate_size=self.intermediate_size, heads=self.heads, kv_heads=self.kv_heads,
+                        head_dim=self.head_dim, theta=self.theta, eps=self.eps)
+
+    def recipe(config):
+        def norm(name):
+            return PartSpec("rmsnorm", dict(name=name, hidden_size=config.hidden_size, eps=config.eps))
+
+        def feed_forward(i):
+            kind = "two_experts" if i % 2 else "swiglu"
+            return PartSpec(kind, dict(prefix=f"layers.{i}.mlp.", hidden_size=config.hidden_size, intermediate_size=config.intermediate_size))
+
+        layers = [
+            PartSpec("pre_norm_residual", dict(
+                mixer=PartSpec("gqa_attention", dict(
+                    prefix=f"layers.{i}.attn.", hidden_size=config.hidden_size, q_heads=config.heads, kv_heads=config.kv_heads,
+                    head_dim=config.head_dim, qkv_bias=False,
+                    position=PartSpec("squashed_rotary", dict(head_dim=config.head_dim, theta=config.theta, factor=4.0)))),
+                feed_forward=feed_forward(i), mixer_norm=norm(f"layers.{i}.norm1"), feed_forward_norm=norm(f"layers.{i}.norm2")))
+            for i in range(config.num_hidden_layers)
+        ]
+        # Layer 0 runs twice, the second time with a cache of its own.
+        order = [LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2)] + [LayerCall(i, i + 1) for i in range(2, config.num_hidden_layers)]
+        return ModelRecipe(
+            config=config,
+            embedding=PartSpec("token_embedding", dict(name="embed", vocab_size=config.vocab_size, hidden_size=config.hidden_size)),
+            layers=layers, final_norm=norm("norm"), schedule=order,
+            head=PartSpec("linear_head", dict(name="head", vocab_size=config.vocab_size, hidden_size=config.hidden_size)))
+
+    register_part("position", "squashed_rotary", SquashedRotary, replace=True)
+    register_part("feed_forward", "two_experts", TwoExperts, replace=True)
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig.from_json_dict, recipe, replace=True)
+    return RoutedConfig
+
+
+def routed_plain(config, weights, tokens):
+    positions = np.arange(len(tokens), dtype=np.float32) / np.float32(4.0)
+    x = weights["embed.weight"][tokens]
+    heads, kv_heads, d = config["heads"], config["kv_heads"], config["head_dim"]
+    for i in [0, 1, 0] + list(range(2, config["num_hidden_layers"])):
+        p = f"layers.{i}."
+        h = plain.rms_norm(x, weights[p + "norm1.weight"], config["eps"])
+        q = plain.linear(h, weights[p + "attn.q_proj.weight"]).reshape(len(tokens), heads, d)
+        k = plain.linear(h, weights[p + "attn.k_proj.weight"]).reshape(len(tokens), kv_heads, d)
+        v = plain.linear(h, weights[p + "attn.v_proj.weight"]).reshape(len(tokens), kv_heads, d)
+        q, k = plain.rope(q, positions, config["theta"]), plain.rope(k, positions, config["theta"])
+        x = x + plain.linear(plain.attention(q, k, v, d**-0.5), weights[p + "attn.o_proj.weight"])
+        h = plain.rms_norm(x, weights[p + "norm2.weight"], config["eps"])
+        if i % 2:
+            probs = plain.softmax(h @ weights[p + "mlp.router.weight"].T)
+            choice = probs.argmax(-1)
+            out = np.zeros_like(x)
+            for t, e in enumerate(choice):
+                w = [weights[f"{p}mlp.experts.{e}.{n}.weight"] for n in ("gate", "up", "down")]
+                out[t] = probs[t, e] * plain.swiglu(h[t : t + 1], *w)[0]
+            x = x + out
+        else:
+            x = x + plain.swiglu(h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, weights["norm.weight"], config["eps"]), weights["head.weight"])
+
+
+def test_toy_position_encoding_and_routed_feed_forward_without_touching_the_framework(tmp_path):
+    from helpers import plain_weights
+    from llm_inference_b200 import create_engine
+    from llm_inference_b200.weights import write_model_folder
+
+    RoutedConfig = register_routed_toy()
+    config = RoutedConfig("ToyRoutedForCausalLM", 131, 64, 3, 96, (), 48, 4, 2, 16, 500.0, 1e-5)
+    folder = write_model_folder(tmp_path / "routed", config, seed=3, std=0.3)
+    raw, weights = plain_weights(folder)
+    rng = np.random.default_rng(4)
+    a = [int(t) for t in rng.integers(0, 131, 37)]
+    b = [int(t) for t in rng.integers(0, 131, 11)]
+    with create_engine(folder, dtype="float32", max_num_sequences=3, kv_cache_bytes=1 << 20, page_size=8,
+                       prefill_chunk_size=5, prefill_burst_size=9) as engine:
+        # Layer 0 is called twice: four caches for three layers.
+        assert sum(len(g.entries) for g in engine.cache.groups) == 4
+        np.testing.assert_allclose(engine.prefill_logits(a), routed_plain(raw, weights, a)[-1], atol=2e-4)
+        ids = [engine.submit(a, 4), engine.submit(b, 4)]
+        while engine.has_work():
+            engine.step()
+        for rid, prompt in zip(ids, (a, b)):
+            tokens, out = list(prompt), []
+            for _ in range(4):
+                out.append(int(np.argmax(routed_plain(raw, weights, tokens)[-1])))
+                tokens.append(out[-1])
+            assert engine.request(rid).output == out
