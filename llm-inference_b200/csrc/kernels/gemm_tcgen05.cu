@@ -175,8 +175,15 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     }
     mbar_init(&accum_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The thread that made the barriers also loads: the weights of the first stages are on
+    // their way before the block has even met (they depend on nothing that runs before).
+    const int first = min(num_kb, stages);
+    for (int i = 0; i < first; ++i) {
+      mbar_expect_tx(&full_bar[i], w_bytes + x_bytes);
+      tma_load_2d(tiles + i * stage_bytes, &w_map, &full_bar[i], (kb_begin + i) * kBlockK, n0);
+    }
   }
-  if (warp == 0) {
+  if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_shared)),
                  "r"(static_cast<uint32_t>(p.tmem_cols))
                  : "memory");
@@ -190,12 +197,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   prefetch_slice_to_l2(p.next_weights, p.next_bytes);
   if (warp == 0 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------------
-    // Weights of the first stages go out before the dependency wait; X follows it.
+    // The weights of the first stages went out above; X follows the dependency wait.
     const int first = min(num_kb, stages);
-    for (int i = 0; i < first; ++i) {
-      mbar_expect_tx(&full_bar[i], w_bytes + x_bytes);
-      tma_load_2d(tiles + i * stage_bytes, &w_map, &full_bar[i], (kb_begin + i) * kBlockK, n0);
-    }
     wait_for_predecessor();
     let_successor_start();
     for (int i = 0; i < first; ++i)
@@ -342,7 +345,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(p.tmem_cols))
                  : "memory");
