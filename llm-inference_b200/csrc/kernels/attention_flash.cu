@@ -521,8 +521,8 @@ template <int HEAD_DIM>
 __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
                                    const float* __restrict__ partial_ml,
                                    __nv_bfloat16* __restrict__ out, int splits) {
-  wait_for_predecessor();
   let_successor_start();
+  wait_for_predecessor();
   const int64_t row = blockIdx.x;
   const float2* ml = reinterpret_cast<const float2*>(partial_ml + row * splits * 2);
   if (splits <= kMaxClusterSplits && HEAD_DIM <= static_cast<int>(blockDim.x)) {

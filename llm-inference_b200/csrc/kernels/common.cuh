@@ -35,9 +35,13 @@ int b200_check_launch(const char* what);
 // Programmatic dependent launch. A kernel launched through `launch_kernel` with overlap
 // enabled may start while its predecessor on the stream is still running; it must call
 // `wait_for_predecessor()` before it reads anything the predecessor wrote or writes anything
-// at all, and may read constants (weights) before that. `let_successor_start()` tells the
-// scheduler that the next kernel on the stream may be made resident as soon as there is
-// room. In a kernel launched the ordinary way both calls do nothing.
+// at all, and may read constants (weights) and the step's metadata before that.
+// `let_successor_start()` tells the scheduler that the next kernel on the stream may be made
+// resident as soon as every block of this one has said so and there is room; the kernels of
+// the decode chain say so first thing, before their own wait, so that a kernel's successor
+// can fetch its weights while the kernel itself still waits for its predecessor (a successor
+// waits for the whole of its predecessor, which waited for its own, so the order of the
+// chain is kept). In a kernel launched the ordinary way both calls do nothing.
 __device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_successor_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

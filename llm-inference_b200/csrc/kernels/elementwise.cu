@@ -141,6 +141,7 @@ __global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__
   // The weights are constants and the row list is part of the step's metadata: both are read
   // before the wait for the kernel in front. After it, everything else this thread reads (its
   // piece of the row and of the pending branch output) is requested before anything is used.
+  let_successor_start();
   float4 v[kNormVecCache], d[kNormVecCache], w[kNormVecCache];
 #pragma unroll
   for (int j = 0; j < kNormVecCache; ++j) {

@@ -109,6 +109,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     }
   };
 
+  let_successor_start();
   // Weights do not depend on the previous kernel: request them first, then wait for it.
 #pragma unroll
   for (int i = 0; i < kStages; ++i) fetch_w(c_begin + i, i);

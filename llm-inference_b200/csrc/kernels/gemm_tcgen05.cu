@@ -169,6 +169,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   const int num_kb = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
+    let_successor_start();
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);

@@ -23,6 +23,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
                                      int kv_heads, int head_dim, int rot, int page_size,
                                      int write_kv, int* __restrict__ err) {
+  let_successor_start();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0 .. q_heads + 2 * kv_heads
   const int rotated_heads = q_heads + kv_heads;
