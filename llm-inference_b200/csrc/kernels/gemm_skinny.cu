@@ -29,7 +29,12 @@ namespace {
 constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
 constexpr int kChunk = 32;   // k per slab
-constexpr int kStages = 8;   // slabs in flight per warp
+// Slabs in flight per warp: 12 for up to 8 tokens, 8 for up to 16 (whose slabs carry one more
+// piece). Measured in the 1.5B decode step: 8 -> 12 saves 3 % at batch 8, costs 2 % at batch 16.
+template <int MT>
+struct SkinnyStages {
+  static constexpr int value = MT == 1 ? 12 : 8;
+};
 
 enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
 
@@ -78,6 +83,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
   const int rg = warp % row_groups, ks = warp / row_groups;
   const int block_rows = row_groups * 16;
   const int n0 = blockIdx.x * block_rows + rg * 16;
+  constexpr int kStages = SkinnyStages<MT>::value;
   uint4* my_ring = ring + static_cast<int64_t>(warp) * kStages * kPieces * 32;
 
   // K is cut first across the blocks of a column (gridDim.y), then across this block's warps.
@@ -240,7 +246,7 @@ int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M
                   const void* next_weights = nullptr, long long next_bytes = 0) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
-  const size_t ring = static_cast<size_t>(kSkinnyWarps) * kStages * (2 + MT) * 32 * 16;
+  const size_t ring = static_cast<size_t>(kSkinnyWarps) * SkinnyStages<MT>::value * (2 + MT) * 32 * 16;
   const size_t sums = static_cast<size_t>(k_splits) * block_rows * MT * 8 * sizeof(float);
   const size_t smem = ring > sums ? ring : sums;
   static bool configured = false;
