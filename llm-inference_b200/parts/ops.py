@@ -103,8 +103,12 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
     # a long one (down: K = 8960 or 18944), which the tcgen05 kernel splits over a cluster,
     # stay here up to 64 rows (32 rows 10.2 vs 13.1 us, 64 rows 11.8 vs 13.2 us; at 128 rows
     # 15.5 vs 13.3 us the library wins again).
+    # Inside a decode step the comparison shifts towards the engine's own kernels, which overlap
+    # their neighbours (programmatic dependent launch) where the library's do not: with all
+    # products on the tcgen05 kernel a step of 32 requests takes 1.85 ms against 1.90 ms, one of
+    # 64 requests 2.57 ms against 2.25 ms. So up to 32 rows everything stays here.
     if m > 16:
-        return "stream" if stream and m <= 64 and k >= 4096 else None
+        return "stream" if stream and (m <= 32 or (m <= 64 and k >= 4096)) else None
     weight_bytes = 2 * n * k
     if skinny and weight_bytes < (16 << 20):
         return "skinny"
