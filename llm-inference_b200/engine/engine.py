@@ -98,8 +98,11 @@ class Engine:
         num_pages: int | None = None,
         cuda_graphs: bool = True,
         run_ahead: bool = True,
+        kernels: str = "tuned",
         model: Model | None = None,
     ) -> None:
+        if kernels not in ("tuned", "plain"):
+            raise ValueError(f"kernels={kernels!r}; expected 'tuned' or 'plain'")
         if max_num_sequences <= 0 or kv_cache_bytes <= 0 or page_size <= 0:
             raise ValueError("sequences, cache bytes and page size must be positive")
         if not 0 < prefill_chunk_size <= prefill_burst_size:
@@ -141,7 +144,12 @@ class Engine:
             model,
             self.cache,
             max_batch_tokens=self.max_batch_tokens,
-            options={"cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens},
+            # "plain": the plain attention kernel and the library's matrix products everywhere (the
+            # slow, simple kernels the tuned ones are checked against); "tuned": each step's best.
+            options={
+                "cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens,
+                **({"attention": "plain", "gemm": "library"} if kernels == "plain" else {}),
+            },
         )
         self.sampler = Sampler(self.device, max_num_sequences)
         # While a decode step's tokens travel to the host, the next step may already run (see

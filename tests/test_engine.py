@@ -80,6 +80,20 @@ def test_bfloat16_greedy_follows_plain_until_a_near_tie(tiny):
         tokens.append(token)
 
 
+def test_plain_kernels_option_gives_the_same_greedy_tokens(tiny):
+    """`kernels="plain"`: plain attention and library products instead of the tuned kernels."""
+    name, folder, config, weights = tiny
+    prompt = random_tokens(np.random.default_rng(8), config["vocab_size"], 19)
+    want = plain.greedy(config, weights, prompt, 12)
+    with engine_for(name, folder, kernels="plain") as engine:
+        assert engine.generate(prompt, 12) == want
+    with engine_for(name, folder, dtype="bfloat16", kernels="plain") as slow, engine_for(name, folder, dtype="bfloat16") as fast:
+        a, b = slow.prefill_logits(prompt), fast.prefill_logits(prompt)
+        assert np.abs(a - b).max() <= 2 * TOLERANCE["bfloat16"]
+    with pytest.raises(ValueError):
+        engine_for(name, folder, kernels="fastest")
+
+
 def test_batched_requests_match_running_alone(tiny):
     name, folder, config, weights = tiny
     vocab = config["vocab_size"]
