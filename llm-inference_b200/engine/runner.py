@@ -155,6 +155,13 @@ class ModelRunner:
         # query per request take the front of the batch.
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         starts = [manager.length(e.request_id) for e in entries]
+        longest = self.cache.max_pages_per_request * self.cache.page_size
+        for e, start in zip(entries, starts):
+            if start + len(e.tokens) > longest:
+                raise ValueError(
+                    f"request {e.request_id} would hold {start + len(e.tokens)} tokens; the cache was built for "
+                    f"requests of at most {longest} (the model's position limit or the pool's size)"
+                )
         for e, start in zip(entries, starts):
             manager.ensure(e.request_id, start + len(e.tokens))
         self.cache.clear_new_slots()

@@ -130,7 +130,7 @@ def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: 
     return True
 
 
-_GEMM_SCRATCH: dict[tuple[str, int, int, int], tuple[int, int]] = {}
+_GEMM_SCRATCH: dict[tuple[str, int, int, int], tuple[int, int]] = {}  # (kernel, m, n, k) -> (floats, counters)
 
 
 def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
@@ -140,7 +140,7 @@ def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Te
 
     m, k = x.shape
     n = weight.shape[0]
-    key = (kernel, (m + 15) // 16, n, k)
+    key = (kernel, m, n, k)
     need = _GEMM_SCRATCH.get(key)
     if need is None:
         floats, counters = c_int64(0), c_int(0)

@@ -146,12 +146,74 @@ def test_mixed_batches_with_page_reuse(tiny, dtype, tmp_path):
     steps, rows = mixed_trace(sequences)
     assert max(len(s["entries"]) for s in steps) >= 3
     assert any(len(e["tokens"]) > 1 for s in steps for e in s["entries"] if len(s["entries"]) > 1)
-    # Room for the four longest at once: far less than all requests together, so pages of
-    # finished requests must be handed out again.
-    longest = sorted((len(t) for t in sequences.values()), reverse=True)
-    pool = pool_for((longest * 2)[:4])
+    # Exactly what the live requests hold at the trace's fullest step: far less than all
+    # requests together, so pages of finished requests must be handed out again.
+    pool = peak_tokens(steps)
     assert pool < pool_for([len(t) for t in sequences.values()] * 2)
     logits = run_trace(folder, dtype, steps, tmp_path / "mixed", pool, PAGE_SIZE[name])
     got = np.concatenate([logits[s["step"]] for s in steps if s["step"] in logits])
     want = np.stack([expected[k][row] for k, row in rows])
     compare(got, want, dtype, f"{name} mixed")
+
+
+def peak_tokens(steps) -> int:
+    """What the live requests hold at the trace's fullest step, each rounded up to 64."""
+    held, peak = {}, 0
+    for step in steps:
+        for e in step["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        peak = max(peak, pool_for(held.values()))
+        for k in step["end"]:
+            del held[k]
+    return peak
+
+
+# Sizes far from the two tiny configurations: many heads over a narrow width with wide heads
+# (the output projection's inner size is a hundred times its outer one), and the smallest heads.
+OTHER_SIZES = {
+    "wide_heads": dict(
+        TINY["B"], hidden_size=40, head_dim=192, num_attention_heads=21, num_key_value_heads=3, intermediate_size=520,
+        vocab_size=257, num_hidden_layers=2, sliding_window=17, max_window_layers=1, rms_norm_eps=3e-6,
+    ),
+    "small_heads": dict(
+        TINY["A"], hidden_size=264, head_dim=16, num_attention_heads=5, num_key_value_heads=1, intermediate_size=56,
+        vocab_size=1537, num_hidden_layers=1, rope_theta=500000.0, max_position_embeddings=256,
+    ),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", list(OTHER_SIZES))
+def test_other_sizes_mixed_with_default_pages(sizes, dtype, tmp_path):
+    """The mixed trace at sizes unlike the tiny configurations', with the default page size
+    and a pool of exactly the trace's peak."""
+    folder = make_model_folder(tmp_path / "model", OTHER_SIZES[sizes], seed=31)
+    config, weights = plain_weights(folder)
+    rng = np.random.default_rng(9)
+    sequences = {f"r{i}": random_tokens(rng, config["vocab_size"], n) for i, n in enumerate([131, 33, 40, 200])}
+    expected = {key: plain.forward(config, weights, tokens) for key, tokens in sequences.items()}
+    steps, rows = mixed_trace(sequences)
+    logits = run_trace(folder, dtype, steps, tmp_path / "out", peak_tokens(steps))
+    got = np.concatenate([logits[s["step"]] for s in steps if s["step"] in logits])
+    compare(got, np.stack([expected[k][row] for k, row in rows]), dtype, f"{sizes} mixed")
+
+
+def test_a_request_past_the_position_limit_is_refused(tmp_path):
+    """Replay stops with a message that names the request and the limit, not with a wrong result."""
+    import json
+    import subprocess
+    import sys
+
+    from helpers import TRACE_RUN
+
+    folder = make_model_folder(tmp_path / "model", TINY["A"], seed=3)
+    limit = TINY["A"]["max_position_embeddings"]
+    steps = [
+        {"step": 0, "entries": [{"id": "long", "tokens": [1] * limit, "want": [limit - 1]}], "end": []},
+        {"step": 1, "entries": [{"id": "long", "tokens": [1], "want": [0]}], "end": ["long"]},
+    ]
+    cmd = [sys.executable, str(TRACE_RUN), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path / "out"), "--max-tokens", "256"]
+    result = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert result.returncode != 0
+    assert "done 0" in result.stdout and "done 1" not in result.stdout
+    assert "would hold 129 tokens" in result.stderr and "at most 128" in result.stderr
