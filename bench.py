@@ -159,7 +159,11 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (both numbers are reported)")
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (both numbers are reported)")
+    parser.add_argument(
+        "--model", choices=["qwen2.5-1.5b", "qwen2.5-7b", "qwen2.5-14b"], default="qwen2.5-1.5b",
+        help="layer sizes of another Qwen2.5 shape (the default is the headline configuration)",
+    )
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     parser.add_argument("--no-graphs", action="store_true")
     args = parser.parse_args()
@@ -185,7 +189,15 @@ def main() -> int:
         return 1
     torch.cuda.set_device(0)
     peak = peaks()
-    raw = dict(MODEL, num_hidden_layers=args.layers, max_window_layers=args.layers)
+    shape = MODEL
+    if args.model != "qwen2.5-1.5b":
+        from llm_inference_b200.cli.presets import PRESETS
+
+        shape = PRESETS[args.model]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    shape_name = args.model.replace("qwen", "Qwen").replace("b", "B") + " shape"
+    raw = dict(shape, num_hidden_layers=args.layers, max_window_layers=args.layers)
     _, config = parse_config(raw)
     model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
     max_batch = max(64, args.batch)
@@ -312,7 +324,7 @@ def main() -> int:
 
     achieved = main_point["bytes"] / (main_point["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": "decode tok/s (batch 8, 2,048-token prompts, Qwen2.5-1.5B shape)",
+        "metric": f"decode tok/s (batch {args.batch}, 2,048-token prompts, {shape_name})",
         "value": main_point["tokens_per_s"],
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -326,9 +338,9 @@ def main() -> int:
         "data": "synthetic: seeded random weights N(0,0.02), token ids uniform in the vocabulary",
         "impl": "ours",
         "config": {
-            "model": "Qwen2.5-1.5B shape",
+            "model": shape_name,
             "layers": args.layers,
-            "layers_full": FULL_LAYERS,
+            "layers_full": full_layers,
             "hidden": config.hidden_size,
             "q_heads": config.num_attention_heads,
             "kv_heads": config.num_key_value_heads,

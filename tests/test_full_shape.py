@@ -19,7 +19,7 @@ SHAPE = {
 }
 
 
-def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto") -> np.ndarray:
+def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto", shape: dict | None = None) -> np.ndarray:
     import torch
 
     from llm_inference_b200 import models  # noqa: F401  (registers the architecture)
@@ -28,7 +28,7 @@ def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto") -> np
     from llm_inference_b200.engine.loading import random_model
     from llm_inference_b200.engine.runner import StepEntry
 
-    settings = dict(SHAPE, use_sliding_window=window > 0, sliding_window=window if window else 32768)
+    settings = dict(shape or SHAPE, use_sliding_window=window > 0, sliding_window=window if window else 32768)
     _, config = parse_config(settings)
     model = random_model(config, 5, dtype, "cuda:0", std=0.05)
     engine = Engine(
@@ -36,7 +36,7 @@ def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto") -> np
         prefill_burst_size=1024, max_batch_tokens=1100, dtype=dtype, cuda_graphs=False,
     )
     engine.runner.options.update(attention=attention, gemm=gemm)
-    prompt = [int(t) for t in np.random.default_rng(0).integers(0, SHAPE["vocab_size"], 700)]
+    prompt = [int(t) for t in np.random.default_rng(0).integers(0, settings["vocab_size"], 700)]
     engine.cache.open(1)
     rows = [engine.runner.step([StepEntry(1, prompt[:517], (516,))])]
     rows.append(engine.runner.step([StepEntry(1, prompt[517:], (len(prompt) - 518,))]))
@@ -69,3 +69,22 @@ def test_benchmark_sized_layers_in_bfloat16_follow_the_32_bit_path(window):
     baseline = np.abs(results["plain+library"] - reference).mean()
     for name in ("tcgen05", "flash"):
         assert np.abs(results[name] - reference).mean() <= 1.1 * baseline, name
+
+
+LARGER = {
+    "7B": dict(SHAPE, num_hidden_layers=2, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, vocab_size=152064, tie_word_embeddings=False),
+    "14B": dict(SHAPE, num_hidden_layers=2, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=13824, vocab_size=152064, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("name", list(LARGER))
+def test_layers_of_the_larger_shapes_follow_the_32_bit_path(name):
+    """Two layers of the Qwen2.5-7B and -14B sizes, the kernels the engine picks by itself."""
+    reference = logits_of("float32", "auto", 0, shape=LARGER[name])
+    got = logits_of("bfloat16", "auto", 0, shape=LARGER[name])
+    scale = float(reference.std())
+    error = np.abs(got - reference)
+    assert error.mean() <= 0.03 * scale and error.max() <= 0.2 * scale, (error.mean(), error.max(), scale)
+    assert (got.argmax(axis=1) == reference.argmax(axis=1)).all()
