@@ -26,7 +26,10 @@
 // (python/instinct/backends/dense.py:124-128).
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -392,11 +395,83 @@ struct StreamPlan {
   size_t smem;
 };
 
-// A function of N, K and the padded token count only (see gemm_skinny.cu for why not of M):
-// about two blocks per SM, each with a ring of at most half an SM's shared memory, so that the
-// blocks of the next kernel on the stream can move in and request their weights while this
-// one drains (measured on a B200: 6% off a whole decode step against one block of 200 KB).
-StreamPlan plan_stream(int N, int K, int tokens_pad) {
+// The kernel's opt-ins, each asked for once (or once per larger size).
+bool allow_shared_memory(size_t bytes) {
+  static size_t allowed = 0;
+  if (bytes > allowed) {
+    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) !=
+        cudaSuccess)
+      return false;
+    allowed = bytes;
+  }
+  return true;
+}
+
+bool allow_wide_clusters() {
+  static bool allowed = false;
+  if (!allowed) {
+    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+      return false;
+    allowed = true;
+  }
+  return true;
+}
+
+void size_ring(StreamPlan& plan, int k_blocks, int tokens_pad) {
+  const size_t x_stride = (static_cast<size_t>(tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
+  const size_t stage = static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride;
+  const int total = plan.blocks * plan.members;
+  const size_t budget = total <= 296 ? 100 * 1024 : 66 * 1024;
+  const int per_block = (k_blocks + plan.members - 1) / plan.members;
+  int stages = static_cast<int>(budget / stage);
+  if (const char* forced = getenv("B200_STREAM_STAGES")) stages = atoi(forced);
+  stages = stages > kMaxStages ? kMaxStages : stages;
+  stages = stages > per_block ? per_block : stages;
+  plan.stages = stages < 2 ? 2 : stages;
+  const size_t partial = static_cast<size_t>(tokens_pad) * kBlockRows * sizeof(float);
+  const size_t ring = plan.stages * stage;
+  plan.smem = (ring > partial ? ring : partial) + 1024;
+}
+
+// How many clusters of `members` blocks the device holds at once when every SM takes one
+// block (clusters do not straddle GPCs, so this is less than SMs / members); 0 if the question
+// cannot be answered. Plans are remembered, so this runs once per shape.
+int clusters_one_per_sm(int members) {
+  if (!allow_shared_memory(48 * 1024) || (members > 8 && !allow_wide_clusters())) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, members * 64);
+  config.blockDim = dim3(kThreadsT);
+  config.dynamicSmemBytes = 48 * 1024;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = members;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, stream_gemm_kernel, &config) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
+}
+
+// A lower bound on the clusters of `members` blocks of `smem` bytes that run at once. The
+// occupancy call answers for one block per SM whatever the block's size, while the profiler's
+// launch statistics and the timings say that blocks of 93 KB run two to an SM. With s blocks
+// per SM a GPC of g SMs takes floor(s g / members) clusters, which is what one block per SM
+// gives for clusters of members / s blocks; rounding that size up keeps the bound safe.
+int clusters_in_flight(int members, size_t smem) {
+  int per_sm = static_cast<int>((227 * 1024) / (smem + 2048));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+  return clusters_one_per_sm((members + per_sm - 1) / per_sm);
+}
+
+StreamPlan plan_stream_uncached(int N, int K, int tokens_pad) {
   StreamPlan plan;
   plan.blocks = (N + kBlockRows - 1) / kBlockRows;
   const int k_blocks = (K + kBlockK - 1) / kBlockK;
@@ -410,19 +485,42 @@ StreamPlan plan_stream(int N, int K, int tokens_pad) {
   int members = max(1, min(min(widest, kMaxMembers), target / plan.blocks));
   while (members > 1 && k_blocks / members < 3) --members;  // every block keeps a few stages to stream
   plan.members = members;
-  const size_t x_stride = (static_cast<size_t>(tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
-  const size_t stage = static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride;
-  const int total = plan.blocks * members;
-  const size_t budget = total <= 296 ? 100 * 1024 : 66 * 1024;
-  const int per_block = (k_blocks + members - 1) / members;
-  int stages = static_cast<int>(budget / stage);
-  if (const char* forced = getenv("B200_STREAM_STAGES")) stages = atoi(forced);
-  stages = stages > kMaxStages ? kMaxStages : stages;
-  stages = stages > per_block ? per_block : stages;
-  plan.stages = stages < 2 ? 2 : stages;
-  const size_t partial = static_cast<size_t>(tokens_pad) * kBlockRows * sizeof(float);
-  const size_t ring = plan.stages * stage;
-  plan.smem = (ring > partial ? ring : partial) + 1024;
+  size_ring(plan, k_blocks, tokens_pad);
+  // All clusters should run at once: one that has to wait for a place starts when the others
+  // are done, and the product takes half as long again (40 row blocks in clusters of 7 took
+  // 16.5 us where clusters of 6 took 11.6 us; 36 in clusters of 8 12.0 us, of 6 8.7 us).
+  // Narrow the clusters until they do.
+  if (members > 1 && !getenv("B200_STREAM_MEMBERS")) {
+    StreamPlan narrower = plan;
+    while (narrower.members > 1) {
+      const int room = clusters_in_flight(narrower.members, narrower.smem);
+      if (getenv("B200_STREAM_DEBUG"))
+        fprintf(stderr, "stream plan N=%d K=%d: %d blocks, clusters of %d (%zu B): room for %d\n", N, K, narrower.blocks,
+                narrower.members, narrower.smem, room);
+      if (room == 0 || narrower.blocks <= room) break;
+      --narrower.members;
+      size_ring(narrower, k_blocks, tokens_pad);
+    }
+    // Clusters of one block never all fit when wider ones did not; then width is not the matter.
+    if (narrower.members > 1) plan = narrower;
+  }
+  return plan;
+}
+
+// The plan is a function of N, K and the padded token count only (see gemm_skinny.cu for why
+// not of M): about two blocks per SM, each with a ring of at most half an SM's shared memory,
+// so that the blocks of the next kernel on the stream can move in and request their weights
+// while this one drains (measured on a B200: 6% off a whole decode step against one block of
+// 200 KB). Plans are remembered: the occupancy question costs more than a launch.
+StreamPlan plan_stream(int N, int K, int tokens_pad) {
+  struct Entry { int n, k, tokens; StreamPlan plan; };
+  static std::mutex guard;
+  static std::vector<Entry> known;
+  std::lock_guard<std::mutex> lock(guard);
+  for (const Entry& e : known)
+    if (e.n == N && e.k == K && e.tokens == tokens_pad) return e.plan;
+  const StreamPlan plan = plan_stream_uncached(N, K, tokens_pad);
+  known.push_back({N, K, tokens_pad, plan});
   return plan;
 }
 
@@ -470,13 +568,7 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   CUtensorMap w_map, x_map;
   if (make_map(&w_map, W, N, K, kBlockRows) != 0) return -1;
   if (make_map(&x_map, X, M, K, p.tokens_pad) != 0) return -1;
-  static size_t configured = 0;
-  if (plan.smem > configured) {
-    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(plan.smem)) != cudaSuccess)
-      return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", plan.smem);
-    configured = plan.smem;
-  }
+  if (!allow_shared_memory(plan.smem)) return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", plan.smem);
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan.blocks, plan.members);
   config.blockDim = dim3(kThreadsT);
@@ -498,14 +590,8 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   }
   config.attrs = attributes;
   config.numAttrs = count;
-  if (plan.members > 8) {
-    static bool allowed = false;
-    if (!allowed) {
-      if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
-        return b200_fail("stream_gemm: clusters of %d blocks are not available", plan.members);
-      allowed = true;
-    }
-  }
+  if (plan.members > 8 && !allow_wide_clusters())
+    return b200_fail("stream_gemm: clusters of %d blocks are not available", plan.members);
   const cudaError_t status = cudaLaunchKernelEx(&config, stream_gemm_kernel, w_map, x_map, p);
   if (status != cudaSuccess) return b200_fail("stream_gemm: %s", cudaGetErrorString(status));
   return 0;

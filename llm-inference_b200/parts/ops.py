@@ -107,8 +107,12 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
     # their neighbours (programmatic dependent launch) where the library's do not: with all
     # products on the tcgen05 kernel a step of 32 requests takes 1.85 ms against 1.90 ms, one of
     # 64 requests 2.57 ms against 2.25 ms. So up to 32 rows everything stays here.
+    # At the 7B and 14B shapes the same rule holds: steps of 32 requests 3.76 against 4.07 ms
+    # (7B) and 8.06 against 8.30 ms (14B) with the library for every product above 16 rows;
+    # at 64 rows only the down products (K of 8960 and more) are worth keeping (14B: 11.66 ms
+    # against 11.93 ms with q/k/v and o, K = 5120, kept too).
     if m > 16:
-        return "stream" if stream and (m <= 32 or (m <= 64 and k >= 4096)) else None
+        return "stream" if stream and (m <= 32 or (m <= 64 and k >= 8192)) else None
     weight_bytes = 2 * n * k
     if skinny and weight_bytes < (16 << 20):
         return "skinny"
