@@ -84,7 +84,13 @@ def main(argv: list[str] | None = None) -> int:
                 next_id += 1
                 cache.open(ids[name])
             entries.append(StepEntry(ids[name], item["tokens"], item.get("want", ())))
-        logits = runner.step(entries)
+        try:
+            logits = runner.step(entries)
+        except ValueError as error:
+            names = {number: name for name, number in ids.items()}
+            live = ", ".join(f"{e.request_id} = {names[e.request_id]!r}" for e in entries)
+            print(f"trace_run: step {step} refused: {error} (requests by number: {live})", file=sys.stderr)
+            return 1
         if logits.shape[0]:
             host = logits.to("cpu", torch.float32).numpy().astype("<f4", copy=False)
             host.tofile(args.out / f"{step}.f32")
