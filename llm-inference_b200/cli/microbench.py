@@ -151,23 +151,34 @@ def bench_attention(args, decode: bool) -> dict:
     for s, c in enumerate(need):
         tables[s, :c] = order[at : at + c]
         at += c
-    keys = torch.randn(num_pages, kv_heads, page, dim, device="cuda").to(torch.bfloat16)
-    values = torch.randn_like(keys)
     positions = [p for s, r in zip(starts, runs) for p in range(s, s + r)]
     token_seq = [i for i, r in enumerate(runs) for _ in range(r)]
-    ctx = make_ctx(positions, token_seq, starts, runs, {"attention": "plain" if args.plain else args.attention})
+    options = {"attention": "plain" if args.plain else args.attention, "decode_loader": args.loader}
+    if args.splits:
+        options["decode_splits"] = args.splits
+    if args.stages:
+        options["decode_stages"] = args.stages
+    ctx = make_ctx(positions, token_seq, starts, runs, options)
     q = torch.randn(len(positions), q_heads * dim, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
-    view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, args.window)
-    fn = lambda: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5)
+    table = torch.from_numpy(tables).cuda()
+    # --layers N: N arenas of the same geometry, as the layers of a model have; back to back
+    # they exceed the L2 cache when one of them does not.
+    fns = []
+    for _ in range(max(1, args.layers)):
+        keys = torch.randn(num_pages, kv_heads, page, dim, device="cuda").to(torch.bfloat16)
+        values = torch.randn_like(keys)
+        view = CacheView(0, True, keys, values, table, num_pages, tables.shape[1], page, args.window)
+        fns.append(lambda view=view: attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, dim, dim**-0.5))
     # --rotate: back to back inside a CUDA graph, so that neither the host's launch cost nor
-    # the idle gap before a lone launch enters (the cache stays in L2, as it does in a model
-    # step, where the layer's keys were written just before).
-    us = time_back_to_back([fn], 16) if args.rotate else time_launches(fn, args.iters)
+    # the idle gap before a lone launch enters (with one arena the cache stays in L2, as it
+    # does in a small model's step, where the layer's keys were written just before).
+    us = time_back_to_back(fns, 16 * len(fns)) if args.rotate else time_launches(fns[0], args.iters)
     kv_bytes = sum(lens) * kv_heads * dim * 2 * 2
     flops = sum(4.0 * q_heads * dim * r * (s + (r + 1) / 2) for s, r in zip(starts, runs))
     return {"kernel": "decode_attention" if decode else "prefill_attention", "batch": len(lens), "context": args.context,
-            "tokens": len(positions), "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
+            "tokens": len(positions), "loader": args.loader, "splits": args.splits, "stages": args.stages,
+            "layers": args.layers, "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
 
 def main(argv=None) -> int:
@@ -191,6 +202,10 @@ def main(argv=None) -> int:
     parser.add_argument("--window", type=int, default=0)
     parser.add_argument("--plain", action="store_true")
     parser.add_argument("--attention", default="auto", choices=["auto", "flash", "tcgen05"])
+    parser.add_argument("--loader", default="auto", choices=["auto", "tma", "cp_async"], help="how decode attention loads keys and values")
+    parser.add_argument("--splits", type=int, default=0, help="blocks per (request, kv head) in decode attention (0: the engine's rule)")
+    parser.add_argument("--stages", type=int, default=0, help="ring depth of the TMA decode kernel (0: the engine's default)")
+    parser.add_argument("--layers", type=int, default=1, help="attention: rotate over this many arenas")
     parser.add_argument("--iters", type=int, default=20)
     args = parser.parse_args(argv)
     if args.library:

@@ -57,6 +57,7 @@ _SIGNATURES: dict[str, list] = {
     + [c_float, c_int, c_void_p, c_void_p],
     "b200_gemm_f32": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
     "b200_paged_flash_attention": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "b200_paged_decode_attention_tma": [c_void_p] * 8 + [c_int] * 8 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "b200_flash_prefill_tcgen05": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_void_p, c_void_p],
     "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p],
     "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p],
@@ -73,6 +74,8 @@ class KernelLibrary:
         self.lib.b200_abi_version.restype = c_int
         self.lib.b200_flash_attention_supported.argtypes = [c_int] * 5
         self.lib.b200_flash_attention_supported.restype = c_int
+        self.lib.b200_decode_attention_tma_supported.argtypes = [c_int] * 4
+        self.lib.b200_decode_attention_tma_supported.restype = c_int
         self.lib.b200_flash_prefill_tcgen05_supported.argtypes = [c_int] * 5
         self.lib.b200_flash_prefill_tcgen05_supported.restype = c_int
         self.lib.b200_skinny_gemm_supported.argtypes = [c_int] * 4

@@ -1,7 +1,8 @@
 """Chooses the attention kernel for a step.
 
 In bfloat16, with a head size and page size the tensor-core kernels take, the step's
-single-token requests (which lead the batch) go to the split-key decode kernel (mma.sync) and
+single-token requests (which lead the batch) go to a split-key decode kernel (mma.sync; keys
+and values by TMA when head_dim is 128 and pages hold 64 rows or more, by cp.async otherwise) and
 the prompt portions to the tcgen05 / TMEM kernel (head_dim 128, pages of at least 16 rows) or
 else to the mma.sync prefill form. Everything else - float32, other head sizes, pages whose
 size is no power of two - runs the plain kernel, which takes every shape.
@@ -43,7 +44,8 @@ def attend(
         decode_seqs = 0  # more than 16 query heads per kv head: the prefill form handles one-token runs too
     if decode_seqs:
         reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
-        splits = ops.decode_splits(decode_seqs, kv_heads, reach)
+        tma = ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+        splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(decode_seqs, kv_heads, reach, tma)
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits,

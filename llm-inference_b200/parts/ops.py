@@ -281,19 +281,35 @@ def paged_attention_plain(
 
 
 NUM_SMS = 148
+DECODE_STAGES = 3  # pieces in flight per warp of the TMA decode kernel
 
 
 def flash_attention_supported(ctx: StepContext, q_heads: int, kv_heads: int, head_dim: int, page_size: int, decode: bool) -> bool:
     return bool(ctx.lib.lib.b200_flash_attention_supported(q_heads, kv_heads, head_dim, page_size, 1 if decode else 0))
 
 
-def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int) -> int:
-    """How many blocks cut each request's keys in a decode step: about two waves of blocks
-    (three blocks fit an SM), at least one 64-key tile each, and few enough that the merge
-    of their partial results stays cheap."""
+def decode_uses_tma(ctx: StepContext, num_seqs: int, q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether a decode step's attention runs the kernel whose warps load by TMA: the shape
+    must suit it (head_dim 128, pages of 64 rows or more), and with very few (request, kv
+    head) pairs the splits merge inside a thread-block cluster, which the other kernel does."""
+    loader = ctx.options.get("decode_loader", "auto")
+    if loader == "cp_async" or not ctx.lib.lib.b200_decode_attention_tma_supported(q_heads, kv_heads, head_dim, page_size):
+        _need(loader != "tma", "the TMA decode kernel does not take this shape")
+        return False
+    merge = ctx.options.get("attention_merge", "auto")
+    return loader == "tma" or merge == "scratch" or (merge == "auto" and num_seqs * kv_heads > 4)
+
+
+def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = False) -> int:
+    """How many blocks cut each request's keys in a decode step: at least one 64-key tile
+    each, and few enough that the merge of their partial results stays cheap. The cp.async
+    kernel (three blocks per SM) wants about two waves of blocks. The TMA kernel (rings three
+    deep, two blocks per SM) wants all its blocks resident at once: measured on a B200 at
+    2,048 keys, 64 requests x 2 kv heads take 26 us in 2 splits and 35 us in 6, and 64 x 8
+    take 82 us unsplit."""
     tiles = max(1, (max_kv_len + 63) // 64)
     pairs = max(1, num_seqs * kv_heads)
-    want = 6 * NUM_SMS // pairs  # rounded down: one block too many would start a third wave
+    want = (2 if tma else 6) * NUM_SMS // pairs  # rounded down: one block too many would start another wave
     return max(1, min(tiles, 16, want))
 
 
@@ -327,8 +343,20 @@ def paged_flash_attention(
     merge = ctx.options.get("attention_merge", "auto")
     if merge == "auto":
         merge = "cluster" if num_seqs * kv_heads <= 4 else "scratch"
-    if decode and splits > 1 and (splits > 16 or merge == "scratch"):
+    use_tma = decode and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
+    if decode and splits > 1 and (splits > 16 or merge == "scratch" or use_tma):
         scratch = ctx.buffer("attention_partials", (num_seqs * q_heads * splits * (head_dim + 2),), torch.float32, per_token=False)
+    # Keys and values by TMA into per-warp rings where the shape allows; "cp_async" keeps the
+    # block-wide cp.async tiles.
+    if use_tma:
+        ctx.lib.call(
+            "b200_paged_decode_attention_tma", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
+            ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(num_seqs), c_int(cache.max_pages),
+            c_int(cache.num_pages), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size),
+            c_int(cache.window), c_float(scale), c_int(splits), c_int(int(ctx.options.get("decode_stages", DECODE_STAGES))),
+            ptr(scratch), ptr(ctx.err), ctx.stream,
+        )
+        return out
     ctx.lib.call(
         "b200_paged_flash_attention", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
         ptr(ctx.seq_q_start), ptr(ctx.seq_q_len), ptr(ctx.seq_kv_len), c_int(first_seq), c_int(num_seqs),

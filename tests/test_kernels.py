@@ -329,7 +329,7 @@ def dense_attention(q, k, v, scale, window, start):
     return (torch.softmax(scores, -1) @ v).permute(1, 0, 2).reshape(n, heads * d)
 
 
-def attention_case(dtype, q_heads, kv_heads, head_dim, page, window, starts, runs, seed=5, spike=None):
+def attention_case(dtype, q_heads, kv_heads, head_dim, page, window, starts, runs, seed=5, spike=None, spike_norm=6.0):
     torch.manual_seed(seed)
     seq_lens = [s + r for s, r in zip(starts, runs)]
     tables, num_pages = paged_layout(seq_lens, page, seed=seed)
@@ -345,7 +345,7 @@ def attention_case(dtype, q_heads, kv_heads, head_dim, page, window, starts, run
         seq, key_pos, row = spike
         pg, r = int(tables[seq, key_pos // page]), key_pos % page
         direction = torch.randn(head_dim, device="cuda")
-        direction = direction / direction.norm() * 6
+        direction = direction / direction.norm() * spike_norm
         keys[pg, :, r, :] = direction.to(dtype)
         q[row] = (direction * 3).to(dtype)
         values[pg, :, r, :] = 10.0
@@ -450,6 +450,7 @@ def test_paged_flash_attention(lib, case):
     )
     ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
     ctx.options["attention"] = "flash"
+    ctx.options["decode_loader"] = "cp_async"  # the TMA-fed decode kernel has a test of its own
     view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
     out = torch.full_like(q, float("nan"))
     attention_dispatch.attend(ctx, view, q, out, q_heads, kv_heads, head_dim, head_dim**-0.5)
@@ -473,6 +474,45 @@ def test_paged_flash_attention(lib, case):
                                       first_seq=0, num_seqs=lead, decode=True, max_q_len=1, splits=splits)
             torch.testing.assert_close(out3[:lead].double(), expected[:lead], **tol(torch.bfloat16))
     assert int(ctx.err.item()) == 0
+
+
+TMA_DECODE_CASES = [
+    # q_heads, kv_heads, page, window, starts (one new token each)
+    (12, 2, 64, 0, [300, 0, 63, 64, 700, 15, 16, 48, 2047]),
+    (28, 4, 128, 0, [127, 128, 5, 1000]),
+    (40, 8, 64, 100, [333, 90, 99, 100, 1500]),
+    (16, 1, 256, 70, [700, 69, 70, 2]),
+    (3, 3, 64, 0, [129, 4000]),
+]
+
+
+@pytest.mark.parametrize("case", TMA_DECODE_CASES)
+def test_decode_attention_with_tma_loads(lib, case):
+    """The decode kernel whose warps get their keys and values by TMA: every ring depth, one
+    block per request and several, against dense attention in float64; then one far key that
+    must dominate its row."""
+    from llm_inference_b200.parts import ops
+    from llm_inference_b200.parts.context import CacheView
+
+    q_heads, kv_heads, page, window, starts = case
+    runs = [1] * len(starts)
+    for spike in ((None,) if window else (None, (len(starts) - 1, 3, len(starts) - 1))):
+        q, keys, values, tables, num_pages, positions, token_seq, expected = attention_case(
+            torch.bfloat16, q_heads, kv_heads, 128, page, window, starts, runs, seed=17, spike=spike, spike_norm=9.0
+        )
+        ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
+        ctx.options["decode_loader"] = "tma"
+        ctx.options["attention_merge"] = "scratch"
+        view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
+        for splits, stages in ((1, 2), (1, 6), (3, 2), (3, 3), (7, 4), (40, 2)):
+            ctx.options["decode_stages"] = stages
+            out = torch.full_like(q, float("nan"))
+            ops.paged_flash_attention(ctx, view, q, out, q_heads, kv_heads, 128, 128**-0.5,
+                                      first_seq=0, num_seqs=len(starts), decode=True, max_q_len=1, splits=splits)
+            assert int(ctx.err.item()) == 0
+            torch.testing.assert_close(out.double(), expected, **tol(torch.bfloat16))
+        if spike is not None:
+            assert expected[spike[2]].abs().min() > 9.0
 
 
 TCGEN05_CASES = [
