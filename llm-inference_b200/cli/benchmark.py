@@ -7,7 +7,14 @@ submitted at once, the engine steps until all are done; reports generated tokens
         [--output-length 32 --warmups 5 --repetitions 3 --max-sequences 16 --max-model-length 2048
          --kv-cache-mib 512 --stop-on-eos]
 
-``prompts.json`` is a JSON array of arrays of token ids.
+``prompts.json`` is a JSON array of arrays of token ids. Instead of ``--prompts``, ``--mix N``
+draws N requests with prompt lengths uniform in ``--mix-prompt-lengths LO HI``, output lengths
+uniform in ``--mix-output-lengths LO HI`` and token ids uniform in the vocabulary, from
+``--mix-seed``; with ``--random SHAPE`` in place of ``--model`` no file is needed at all:
+
+    python -m llm_inference_b200.cli.benchmark --random qwen2.5-14b --mix 64 --mix-prompt-lengths 128 4096
+        --mix-output-lengths 128 512 --max-sequences 64 --max-model-length 8192 --kv-cache-mib 60000
+        --prefill-chunk-size 512 --warmups 1 --repetitions 1 --output out.json
 """
 
 from __future__ import annotations
@@ -34,12 +41,29 @@ def percentiles(values: list[float]) -> dict[str, float]:
     return {"p50": pick(0.50), "p95": pick(0.95), "p99": pick(0.99)}
 
 
-def run_once(engine, prompts, output_length: int, eos) -> tuple[list[dict], float]:
+def synthetic_mix(count: int, prompt_lengths, output_lengths, vocab: int, seed: int):
+    """``count`` prompts of random ids with their output lengths, both lengths uniform in the
+    given inclusive ranges."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    prompts, outputs = [], []
+    for _ in range(count):
+        n = int(rng.integers(prompt_lengths[0], prompt_lengths[1] + 1))
+        prompts.append([int(t) for t in rng.integers(0, vocab, n)])
+        outputs.append(int(rng.integers(output_lengths[0], output_lengths[1] + 1)))
+    return prompts, outputs
+
+
+def run_once(engine, prompts, output_length, eos) -> tuple[list[dict], float]:
+    """Submits every prompt at once and steps until all are done. ``output_length`` is one
+    number for all requests or a list with one per prompt."""
     import torch
 
+    lengths = output_length if isinstance(output_length, (list, tuple)) else [output_length] * len(prompts)
     torch.cuda.synchronize()
     begin = time.perf_counter()
-    ids = [engine.submit(p, output_length, eos) for p in prompts]
+    ids = [engine.submit(p, n, eos) for p, n in zip(prompts, lengths)]
     first: dict[int, float] = {}
     last: dict[int, float] = {}
     counts = {i: 0 for i in ids}
@@ -66,7 +90,11 @@ def run_once(engine, prompts, output_length: int, eos) -> tuple[list[dict], floa
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     add_engine_options(parser)
-    parser.add_argument("--prompts", type=Path, required=True, help="JSON array of pre-tokenized integer arrays")
+    parser.add_argument("--prompts", type=Path, default=None, help="JSON array of pre-tokenized integer arrays")
+    parser.add_argument("--mix", type=int, default=0, metavar="N", help="instead of --prompts: N synthetic requests")
+    parser.add_argument("--mix-prompt-lengths", type=int, nargs=2, default=[128, 4096], metavar=("LO", "HI"))
+    parser.add_argument("--mix-output-lengths", type=int, nargs=2, default=[128, 512], metavar=("LO", "HI"))
+    parser.add_argument("--mix-seed", type=int, default=0)
     parser.add_argument("--output", type=Path, required=True)
     parser.add_argument("--output-length", type=int, default=32)
     parser.add_argument("--warmups", type=int, default=5)
@@ -74,14 +102,22 @@ def main(argv=None) -> int:
     parser.add_argument("--stop-on-eos", action="store_true", help="allow EOS to shorten requests")
     args = parser.parse_args(argv)
 
-    prompts = [[int(t) for t in p] for p in json.loads(args.prompts.read_text())]
+    if (args.prompts is None) == (args.mix <= 0):
+        parser.error("give either --prompts FILE or --mix N")
     with engine_from(args) as engine:
+        if args.mix > 0:
+            prompts, output_length = synthetic_mix(
+                args.mix, args.mix_prompt_lengths, args.mix_output_lengths, engine.vocab_size, args.mix_seed
+            )
+        else:
+            prompts = [[int(t) for t in p] for p in json.loads(args.prompts.read_text())]
+            output_length = args.output_length
         eos = engine.eos_token_ids if args.stop_on_eos else ()
         for _ in range(args.warmups):
-            run_once(engine, prompts, args.output_length, eos)
+            run_once(engine, prompts, output_length, eos)
         all_metrics, walls = [], []
         for _ in range(args.repetitions):
-            metrics, wall = run_once(engine, prompts, args.output_length, eos)
+            metrics, wall = run_once(engine, prompts, output_length, eos)
             all_metrics += metrics
             walls.append(wall)
         stats = engine.stats()
@@ -89,7 +125,8 @@ def main(argv=None) -> int:
     result = {
         "implementation": "llm-inference_b200",
         "configuration": {
-            "model_path": str(args.model), "output_length": args.output_length, "warmups": args.warmups,
+            "model_path": str(args.model) if args.model else f"random:{args.random}", "warmups": args.warmups,
+            "output_length": args.output_length if args.mix <= 0 else list(args.mix_output_lengths),
             "repetitions": args.repetitions, "concurrency": len(prompts),
             "prompt_token_lengths": [len(p) for p in prompts], "max_model_length": args.max_model_length,
             "kv_cache_mib": args.kv_cache_mib, "stop_on_eos": args.stop_on_eos, "dtype": args.dtype,

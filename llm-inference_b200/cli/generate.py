@@ -16,7 +16,9 @@ from pathlib import Path
 
 
 def add_engine_options(parser: argparse.ArgumentParser) -> None:
-    parser.add_argument("--model", type=Path, required=True, help="folder with config.json and *.safetensors")
+    parser.add_argument("--model", type=Path, default=None, help="folder with config.json and *.safetensors")
+    parser.add_argument("--random", default=None, metavar="SHAPE", help="instead of --model: a named shape (cli/presets.py) with seeded random weights drawn on the device")
+    parser.add_argument("--weights-seed", type=int, default=0, help="seed of --random's weights")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--max-sequences", type=int, default=16)
     parser.add_argument("--max-model-length", type=int, default=2048)
@@ -32,12 +34,24 @@ def add_engine_options(parser: argparse.ArgumentParser) -> None:
 def engine_from(args):
     from .. import create_engine
 
-    return create_engine(
-        args.model, dtype=args.dtype, max_num_sequences=args.max_sequences, max_model_length=args.max_model_length,
+    options = dict(
+        dtype=args.dtype, max_num_sequences=args.max_sequences, max_model_length=args.max_model_length,
         kv_cache_bytes=args.kv_cache_mib << 20, page_size=args.page_size, prefill_chunk_size=args.prefill_chunk_size,
         prefill_burst_size=max(args.prefill_burst_size, args.prefill_chunk_size), cuda_graphs=not args.no_cuda_graphs,
         run_ahead=not args.no_run_ahead, kernels=args.kernels,
     )
+    if (args.model is None) == (args.random is None):
+        raise SystemExit("give either --model DIR or --random SHAPE")
+    if args.random is not None:
+        from ..config import parse_config
+        from ..engine.loading import random_model
+        from .presets import PRESETS
+
+        if args.random not in PRESETS:
+            raise SystemExit(f"--random {args.random!r}: known shapes are {', '.join(sorted(PRESETS))}")
+        _, config = parse_config(PRESETS[args.random])
+        options["model"] = random_model(config, seed=args.weights_seed, dtype=args.dtype)
+    return create_engine(args.model, **options)
 
 
 def main(argv=None) -> int:

@@ -52,3 +52,19 @@ def test_generate_and_benchmark(tmp_path):
     assert report["aggregate"]["generated_tokens_per_second"] > 0
     assert len(report["requests"]) == 6 and all(r["output_tokens"] == 8 for r in report["requests"])
     assert set(report["aggregate"]["ttft_ms"]) == {"p50", "p95", "p99"}
+
+
+@pytest.mark.gpu
+def test_benchmark_with_a_random_shape_and_a_synthetic_mix(tmp_path):
+    result = tmp_path / "mix.json"
+    run("benchmark", "--random", "tiny-b", "--mix", "5", "--mix-prompt-lengths", "3", "40", "--mix-output-lengths", "2", "9",
+        "--output", str(result), "--warmups", "1", "--repetitions", "1", "--max-sequences", "3", "--max-model-length", "64",
+        "--kv-cache-mib", "1", "--page-size", "8", "--prefill-chunk-size", "16")
+    report = json.loads(result.read_text())
+    requests = report["requests"]
+    assert len(requests) == 5
+    assert all(3 <= r["prompt_tokens"] <= 40 and 2 <= r["output_tokens"] <= 9 for r in requests)
+    assert len({r["prompt_tokens"] for r in requests}) > 1
+    assert report["configuration"]["model_path"] == "random:tiny-b"
+    neither = run("benchmark", "--mix", "2", "--output", str(result), check=False)
+    assert neither.returncode != 0 and "--model DIR or --random SHAPE" in neither.stderr
