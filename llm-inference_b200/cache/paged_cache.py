@@ -117,6 +117,7 @@ class PagedCache:
         else:
             raise ValueError("give the cache a byte budget or a page count")
         self.entry_group: dict[int, tuple[CacheGroup, int]] = {}
+        self._entry_arenas: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
         for group in self.groups:
             spec = group.spec
             group.arena = torch.zeros(
@@ -177,11 +178,14 @@ class PagedCache:
         if cache_id in self.states:
             return CacheView(cache_id=cache_id, writes=writes, state=self.states[cache_id])
         group, slot = self.entry_group[cache_id]
+        arenas = self._entry_arenas.get(cache_id)
+        if arenas is None:  # the arena never moves: slice it once per entry, not once per layer and step
+            arenas = self._entry_arenas[cache_id] = (group.arena[slot, 0], group.arena[slot, 1])
         return CacheView(
             cache_id=cache_id,
             writes=writes,
-            keys=group.arena[slot, 0],
-            values=group.arena[slot, 1],
+            keys=arenas[0],
+            values=arenas[1],
             block_table=block_tables[group.index],
             num_pages=group.capacity_pages + 1,
             max_pages=self.max_pages_per_request,

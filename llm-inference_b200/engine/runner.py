@@ -137,7 +137,8 @@ class ModelRunner:
 
     def step(self, entries: Sequence[StepEntry], *, check: bool = False) -> torch.Tensor:
         """Run one batch; returns ``[wanted, vocab]`` float32 logits on the device, in the
-        order of ``entries`` and of each entry's ``want``."""
+        order of ``entries`` and of each entry's ``want``. They live in scratch memory that the
+        next step reuses: copy what must outlast it."""
         entries = [e for e in entries if len(e.tokens) > 0]
         manager = self.cache.manager
         if not entries:

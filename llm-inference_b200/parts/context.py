@@ -5,8 +5,21 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any
 
+from ctypes import c_void_p
+
 import numpy as np
 import torch
+
+# The raw handle of the current stream without building a Stream object for it (several
+# microseconds per launch otherwise); older builds of the library lack the shortcut.
+_CURRENT_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _raw_stream(device: torch.device) -> int:
+    if _CURRENT_RAW_STREAM is not None:
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        return _CURRENT_RAW_STREAM(index)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 @dataclass
@@ -52,6 +65,8 @@ class Workspace:
     def __init__(self, device: torch.device, min_rows: int = 0) -> None:
         self.device = device
         self._flat: dict[str, torch.Tensor] = {}
+        # (name, dtype, shape) -> the view handed out last time; valid until a buffer moves.
+        self._views: dict[tuple, torch.Tensor] = {}
         # Buffers whose first dimension counts tokens are sized for at least this many rows,
         # so that a later, larger step does not move them.
         self.min_rows = min_rows
@@ -60,6 +75,11 @@ class Workspace:
         self.generation = 0
 
     def get(self, name: str, shape: tuple[int, ...], dtype: torch.dtype, *, per_token: bool = True) -> torch.Tensor:
+        # A step asks for the same few dozen buffers in every layer: the view itself is kept.
+        view_key = (name, dtype, tuple(shape))
+        view = self._views.get(view_key)
+        if view is not None:
+            return view
         count = 1
         for s in shape:
             count *= int(s)
@@ -72,7 +92,12 @@ class Workspace:
             flat = torch.empty(max(capacity, count, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
             self.generation += 1
-        return flat[:count].view(shape)
+            self._views.clear()
+        view = flat[:count].view(shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[view_key] = view
+        return view
 
     def zeros(self, name: str, count: int, dtype: torch.dtype) -> torch.Tensor:
         """A buffer that starts zeroed and whose users leave it zeroed (arrival counters)."""
@@ -123,6 +148,6 @@ class StepContext:
 
     @property
     def stream(self):
-        from ctypes import c_void_p
-
-        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        """The current CUDA stream's handle (looked up at every launch: it changes while a
+        graph is being captured)."""
+        return c_void_p(_raw_stream(self.device))

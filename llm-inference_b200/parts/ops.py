@@ -50,8 +50,9 @@ def linear(
     """``out = x @ weight.T (+ bias)``; ``weight`` is ``[out_features, in_features]``."""
     m, k = x.shape
     n = weight.shape[0]
-    _need(weight.shape[1] == k, f"linear: x is [{m},{k}] but weight is {list(weight.shape)}")
-    _need(tuple(out.shape) == (m, n), f"linear: out is {list(out.shape)}, expected [{m},{n}]")
+    if weight.shape[1] != k or tuple(out.shape) != (m, n):  # the message is built only when needed: this runs per product
+        _need(weight.shape[1] == k, f"linear: x is [{m},{k}] but weight is {list(weight.shape)}")
+        _need(False, f"linear: out is {list(out.shape)}, expected [{m},{n}]")
     _need(x.is_contiguous() and weight.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
     if m == 0:
         return out
@@ -88,6 +89,18 @@ def _small_gemm_kernel(ctx: StepContext, m: int, n: int, k: int, epilogue: int) 
     choice = ctx.options.get("gemm", "auto")
     if choice == "library":
         return None
+    key = (m, n, k, epilogue, choice)
+    if key not in _GEMM_CHOICES:
+        if len(_GEMM_CHOICES) > 4096:
+            _GEMM_CHOICES.clear()
+        _GEMM_CHOICES[key] = _choose_small_gemm(ctx, m, n, k, epilogue, choice)
+    return _GEMM_CHOICES[key]
+
+
+_GEMM_CHOICES: dict[tuple, str | None] = {}  # the rule below is a pure function of its key
+
+
+def _choose_small_gemm(ctx: StepContext, m: int, n: int, k: int, epilogue: int, choice: str) -> str | None:
     stream = bool(ctx.lib.lib.b200_stream_gemm_supported(m, n, k, epilogue))
     skinny = bool(ctx.lib.lib.b200_skinny_gemm_supported(m, n, k, epilogue))
     if choice == "tcgen05":

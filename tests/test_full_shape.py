@@ -38,14 +38,27 @@ def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto", shape
     engine.runner.options.update(attention=attention, gemm=gemm)
     prompt = [int(t) for t in np.random.default_rng(0).integers(0, settings["vocab_size"], 700)]
     engine.cache.open(1)
-    rows = [engine.runner.step([StepEntry(1, prompt[:517], (516,))])]
-    rows.append(engine.runner.step([StepEntry(1, prompt[517:], (len(prompt) - 518,))]))
+    # A step's logits live in a scratch buffer that the next step overwrites: copy them.
+    rows = [engine.runner.step([StepEntry(1, prompt[:517], (516,))]).clone()]
+    rows.append(engine.runner.step([StepEntry(1, prompt[517:], (len(prompt) - 518,))]).clone())
     for token in (11, 222, 3333):
-        rows.append(engine.runner.step([StepEntry(1, (token,), (0,))]))
+        rows.append(engine.runner.step([StepEntry(1, (token,), (0,))]).clone())
     engine.runner.check()
     out = torch.cat(rows).float().cpu().numpy()
     engine.close()
     return out
+
+
+def assert_same_greedy_tokens(got: np.ndarray, reference: np.ndarray, name: str = "") -> None:
+    """Every row picks the token the 32-bit path picks, except at a near-tie: where the 32-bit
+    logits of the two picks lie closer together than four times the row's own mean rounding
+    error, either may win (among 150,000 random logits the best two are often that close)."""
+    assert len({row.tobytes() for row in reference}) == len(reference), "rows must be distinct positions"
+    for r, (mine, theirs) in enumerate(zip(got.argmax(axis=1), reference.argmax(axis=1))):
+        if mine != theirs:
+            margin = float(reference[r, theirs] - reference[r, mine])
+            rounding = float(np.abs(got[r] - reference[r]).mean())
+            assert margin <= 4.0 * rounding, (name, r, int(mine), int(theirs), margin, rounding)
 
 
 @pytest.mark.parametrize("window", [0, 300], ids=["full", "window300"])
@@ -63,7 +76,7 @@ def test_benchmark_sized_layers_in_bfloat16_follow_the_32_bit_path(window):
         # bfloat16 keeps 8 bits: activations rounded a few dozen times on the way cost a few
         # per cent of the logits' spread, whichever kernels run; a wrong tile costs the spread.
         assert error.mean() <= 0.03 * scale and error.max() <= 0.2 * scale, (name, error.mean(), error.max(), scale)
-        assert (got.argmax(axis=1) == reference.argmax(axis=1)).all(), name
+        assert_same_greedy_tokens(got, reference, name)
     # The engine's own kernels are no further from 32-bit than the library product with the
     # plain attention kernel is.
     baseline = np.abs(results["plain+library"] - reference).mean()
@@ -86,5 +99,13 @@ def test_layers_of_the_larger_shapes_follow_the_32_bit_path(name):
     got = logits_of("bfloat16", "auto", 0, shape=LARGER[name])
     scale = float(reference.std())
     error = np.abs(got - reference)
-    assert error.mean() <= 0.03 * scale and error.max() <= 0.2 * scale, (error.mean(), error.max(), scale)
-    assert (got.argmax(axis=1) == reference.argmax(axis=1)).all()
+    # What bfloat16 itself costs at this size is measured, not assumed: the same model with the
+    # plain attention kernel and the library's products. Sums over 13,824 and 18,944 terms leave
+    # the largest of 760,000 rounding errors at a fifth of the logits' spread on that path too
+    # (0.21 at the 14B size); the engine's own kernels must not be further off than that, and a
+    # wrong tile, which costs the spread, is.
+    baseline = np.abs(logits_of("bfloat16", "plain", 0, "library", shape=LARGER[name]) - reference)
+    assert error.mean() <= 0.03 * scale, (error.mean(), scale)
+    assert error.mean() <= 1.1 * baseline.mean(), (error.mean(), baseline.mean())
+    assert error.max() <= 1.25 * baseline.max() and error.max() <= 0.3 * scale, (error.max(), baseline.max(), scale)
+    assert_same_greedy_tokens(got, reference, name)
