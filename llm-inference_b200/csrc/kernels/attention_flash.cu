@@ -1034,7 +1034,8 @@ B200_API int b200_decode_attention_tma_supported(int q_heads, int kv_heads, int 
 // Decode attention for requests [0, num_seqs) of the step, one new token each, with keys and
 // values loaded by TMA into per-warp rings of `stages` pieces (2 to 6). With splits > 1 the
 // partial results go through `scratch` (b200_flash_attention_scratch_floats) and the merge
-// kernel. The arenas must be 16-byte aligned and hold finite numbers in every row of a page
+// kernel, or, without scratch and with at most 16 splits, the splits form a thread-block
+// cluster and merge on chip. The arenas must be 16-byte aligned and hold finite numbers in every row of a page
 // that a block table names, written or not: whole 16-row pieces are loaded and the rows past
 // a request's length are masked by weight zero, not skipped.
 B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena, const void* v_arena, void* out,
@@ -1049,7 +1050,8 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
                head_dim, page_size);
   B200_REQUIRE(num_seqs > 0 && num_seqs <= 65535 && splits >= 1 && splits <= 65535, "decode attention (TMA): bad batch");
   B200_REQUIRE(stages >= 2 && stages <= kTmaMaxStages, "decode attention (TMA): 2 to %d stages, not %d", kTmaMaxStages, stages);
-  B200_REQUIRE(splits == 1 || scratch != nullptr, "decode attention (TMA): splits need scratch");
+  B200_REQUIRE(splits == 1 || scratch != nullptr || splits <= kMaxClusterSplits,
+               "decode attention (TMA): more than %d splits need scratch", kMaxClusterSplits);
   B200_REQUIRE((reinterpret_cast<uintptr_t>(k_arena) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_arena) & 15) == 0,
                "decode attention (TMA): arenas must be 16-byte aligned");
   FlashParams p;
@@ -1073,7 +1075,7 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   p.page_mask = page_size - 1;
   p.window = window;
   p.splits = splits;
-  p.cluster_merge = 0;
+  p.cluster_merge = (scratch == nullptr && splits > 1) ? 1 : 0;
   p.scale_log2 = scale * kLog2e;
   p.err = err;
   p.partial_out = scratch;
@@ -1090,10 +1092,36 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
     configured = true;
   }
   const dim3 grid(splits, kv_heads, num_seqs);
-  cudaError_t status = launch_kernel(paged_decode_tma_kernel, grid, dim3(kFlashThreads), decode_tma_smem_bytes(stages),
-                                     stream, k_map, v_map, p, stages);
+  cudaError_t status;
+  if (p.cluster_merge) {
+    // The splits of a (request, kv head) form one thread-block cluster and merge on chip.
+    static bool wide_clusters = false;
+    if (splits > 8 && !wide_clusters) {
+      if (cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        return b200_fail("decode attention (TMA): clusters of %d blocks are not allowed here", splits);
+      wide_clusters = true;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3(kFlashThreads);
+    config.dynamicSmemBytes = decode_tma_smem_bytes(stages);
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = splits;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = b200_overlap_enabled() ? 2 : 1;
+    status = cudaLaunchKernelEx(&config, paged_decode_tma_kernel, k_map, v_map, p, stages);
+  } else {
+    status = launch_kernel(paged_decode_tma_kernel, grid, dim3(kFlashThreads), decode_tma_smem_bytes(stages), stream,
+                           k_map, v_map, p, stages);
+  }
   if (status != cudaSuccess) return b200_fail("decode attention (TMA): %s", cudaGetErrorString(status));
-  if (splits > 1) {
+  if (splits > 1 && !p.cluster_merge) {
     status = launch_kernel(flash_merge_kernel<kTmaDim>, dim3(num_seqs * q_heads), dim3(128), 0, stream, p.partial_out,
                            p.partial_ml, p.out, splits);
     if (status != cudaSuccess) return b200_fail("decode attention (TMA) merge: %s", cudaGetErrorString(status));

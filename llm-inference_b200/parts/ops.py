@@ -302,15 +302,14 @@ def flash_attention_supported(ctx: StepContext, q_heads: int, kv_heads: int, hea
 
 
 def decode_uses_tma(ctx: StepContext, num_seqs: int, q_heads: int, kv_heads: int, head_dim: int, page_size: int) -> bool:
-    """Whether a decode step's attention runs the kernel whose warps load by TMA: the shape
-    must suit it (head_dim 128, pages of 64 rows or more), and with very few (request, kv
-    head) pairs the splits merge inside a thread-block cluster, which the other kernel does."""
+    """Whether a decode step's attention runs the kernel whose warps load by TMA: whenever
+    the shape suits it (head_dim 128, pages of 64 rows or more), unless
+    ``options["decode_loader"]`` says ``"cp_async"``."""
     loader = ctx.options.get("decode_loader", "auto")
     if loader == "cp_async" or not ctx.lib.lib.b200_decode_attention_tma_supported(q_heads, kv_heads, head_dim, page_size):
         _need(loader != "tma", "the TMA decode kernel does not take this shape")
         return False
-    merge = ctx.options.get("attention_merge", "auto")
-    return loader == "tma" or merge == "scratch" or (merge == "auto" and num_seqs * kv_heads > 4)
+    return True
 
 
 def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = False) -> int:
@@ -349,15 +348,18 @@ def paged_flash_attention(
     _need(q.is_contiguous() and out.is_contiguous(), "flash attention: operands must be contiguous")
     _need(not decode or first_seq == 0, "flash attention: decoded tokens must lead the batch")
     scratch = None
-    # Splits are merged on chip by a thread-block cluster when there are very few (request, kv
-    # head) pairs, otherwise through scratch by a second small kernel: measured on a B200, the
-    # cluster form wins at batch 1 (1.48 vs 1.66 ms per step of the 1.5B shape) and loses from
-    # batch 8 on (1.72 vs 1.65 ms), where clusters of 16 blocks are slow to place.
+    # The cp.async kernel merges its splits on chip by a thread-block cluster when there are
+    # very few (request, kv head) pairs, otherwise through scratch by a second small kernel:
+    # measured on a B200, the cluster form wins at batch 1 (1.48 vs 1.66 ms per step of the
+    # 1.5B shape) and loses from batch 8 on (1.72 vs 1.65 ms), where clusters of 16 blocks are
+    # slow to place. The TMA kernel always goes through scratch unless told otherwise: at
+    # batch 1 both forms take 1.10 ms per step (the cp.async kernel 1.15), at batch 2 scratch
+    # 1.10 and the cluster 1.12, from batch 4 on the cluster loses.
+    use_tma = decode and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
     merge = ctx.options.get("attention_merge", "auto")
     if merge == "auto":
-        merge = "cluster" if num_seqs * kv_heads <= 4 else "scratch"
-    use_tma = decode and decode_uses_tma(ctx, num_seqs, q_heads, kv_heads, head_dim, cache.page_size)
-    if decode and splits > 1 and (splits > 16 or merge == "scratch" or use_tma):
+        merge = "cluster" if num_seqs * kv_heads <= 4 and not use_tma else "scratch"
+    if decode and splits > 1 and (splits > 16 or merge == "scratch"):
         scratch = ctx.buffer("attention_partials", (num_seqs * q_heads * splits * (head_dim + 2),), torch.float32, per_token=False)
     # Keys and values by TMA into per-warp rings where the shape allows; "cp_async" keeps the
     # block-wide cp.async tiles.

@@ -502,10 +502,13 @@ def test_decode_attention_with_tma_loads(lib, case):
         )
         ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
         ctx.options["decode_loader"] = "tma"
-        ctx.options["attention_merge"] = "scratch"
         view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
-        for splits, stages in ((1, 2), (1, 6), (3, 2), (3, 3), (7, 4), (40, 2)):
+        # Splits merged through scratch memory by a second kernel, or on chip by a cluster.
+        for splits, stages, merge in ((1, 2, "scratch"), (1, 6, "scratch"), (3, 2, "scratch"), (3, 3, "scratch"),
+                                      (7, 4, "scratch"), (40, 2, "scratch"), (2, 3, "cluster"), (8, 2, "cluster"),
+                                      (16, 3, "cluster")):
             ctx.options["decode_stages"] = stages
+            ctx.options["attention_merge"] = merge
             out = torch.full_like(q, float("nan"))
             ops.paged_flash_attention(ctx, view, q, out, q_heads, kv_heads, 128, 128**-0.5,
                                       first_seq=0, num_seqs=len(starts), decode=True, max_q_len=1, splits=splits)
