@@ -371,6 +371,8 @@ def paged_flash_attention(
             c_int(cache.window), c_float(scale), c_int(splits), c_int(int(ctx.options.get("decode_stages", DECODE_STAGES))),
             ptr(scratch), ptr(ctx.err), ctx.stream,
         )
+        if scratch is not None:
+            ctx.lib.calls += 1  # the merge kernel is a launch of its own
         return out
     ctx.lib.call(
         "b200_paged_flash_attention", ptr(q), ptr(cache.keys), ptr(cache.values), ptr(out), ptr(cache.block_table),
@@ -379,6 +381,8 @@ def paged_flash_attention(
         c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(cache.page_size), c_int(cache.window), c_float(scale),
         c_int(1 if decode else 0), c_int(splits), ptr(scratch), ptr(ctx.err), ctx.stream,
     )
+    if scratch is not None:
+        ctx.lib.calls += 1  # the merge kernel is a launch of its own
     return out
 
 
