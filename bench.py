@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--model SHAPE] [--batch B] [--prompt-len P] [--context C]
 
 A *step* is one decode step. The default run uses the layer sizes of the Qwen2.5-1.5B shape
 with seeded random bfloat16 weights, eight requests that each hold a 2,048-token prompt and
@@ -87,7 +88,7 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             threading.Thread(target=self._read, daemon=True).start()
@@ -155,7 +156,7 @@ def attention_flops(config, layers: int, tokens: int) -> float:
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=240)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)
@@ -165,6 +166,8 @@ def main() -> int:
         help="layer sizes of another Qwen2.5 shape (the default is the headline configuration)",
     )
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens each request holds before it decodes")
+    parser.add_argument("--context", type=int, default=0, help="longest request the engine is built for (default: twice the prompt)")
     parser.add_argument("--no-graphs", action="store_true")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -174,6 +177,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    prompt_len = args.prompt_len
+    context = args.context or max(CONTEXT, 2 * prompt_len)
 
     import numpy as np
     import torch
@@ -205,10 +210,14 @@ def main() -> int:
     new_tokens = 256
     if steps + warmup + 1 > new_tokens:
         new_tokens = steps + warmup + 1
-    budget_tokens = max_batch * (PROMPT + new_tokens + PAGE)
+    if prompt_len < 1 or context < max(PROMPT, prompt_len + new_tokens) or context > config.max_position_embeddings:
+        print(f"bench.py: --context {context} must hold the {PROMPT}-token prefill and {prompt_len} + {new_tokens} tokens "
+              f"of each request, within the model's {config.max_position_embeddings} positions")
+        return 2
+    budget_tokens = max_batch * (prompt_len + new_tokens + PAGE)
     kv_bytes_per_token = 2 * args.layers * config.num_key_value_heads * config.head_dim * 2
     engine = Engine(
-        model=model, max_num_sequences=max_batch, max_model_length=CONTEXT, kv_cache_bytes=budget_tokens * kv_bytes_per_token,
+        model=model, max_num_sequences=max_batch, max_model_length=context, kv_cache_bytes=budget_tokens * kv_bytes_per_token,
         page_size=PAGE, prefill_chunk_size=PROMPT, prefill_burst_size=PROMPT, max_batch_tokens=PROMPT + max_batch,
         cuda_graphs=not args.no_graphs,
     )
@@ -257,7 +266,8 @@ def main() -> int:
         ids = list(range(20_000 + 1000 * batch, 20_000 + 1000 * batch + batch))
         for rid in ids:
             cache.open(rid)
-            runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, vocab, PROMPT)])])
+            for begin in range(0, prompt_len, PROMPT):  # the prompt goes in by portions of 2,048
+                runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, vocab, min(PROMPT, prompt_len - begin))])])
         feed = rng.integers(0, vocab, size=(w + k, batch))
 
         def one(step: int) -> None:
@@ -280,7 +290,7 @@ def main() -> int:
         ms = start.elapsed_time(end) / k
         replays = runner.graph_replays - replays_before
         launches = (runner.lib.calls - calls_before) + replays * runner.launches_per_graph.get(runner._bucket(batch), 0)
-        mean_context = PROMPT + w + k / 2.0
+        mean_context = prompt_len + w + k / 2.0
         step_bytes = weight_bytes + batch * mean_context * kv_bytes_per_token
         runner.check()
         for rid in ids:
@@ -297,7 +307,7 @@ def main() -> int:
             points[f"decode_b{batch}"] = decode_point(batch, max(16, steps // 2), warmup)["tokens_per_s"]
 
     # --- the same through the public entry point: host tokens in and out ------------------------
-    prompts = [[int(t) for t in rng.integers(0, vocab, PROMPT)] for _ in range(args.batch)]
+    prompts = [[int(t) for t in rng.integers(0, vocab, prompt_len)] for _ in range(args.batch)]
     request_ids = [engine.submit(p, new_tokens) for p in prompts]
     while any(engine.request(r).state.value in ("waiting", "prefilling") for r in request_ids):
         engine.step()
@@ -324,7 +334,7 @@ def main() -> int:
 
     achieved = main_point["bytes"] / (main_point["ms_per_step"] / 1e3) / 1e9
     line = {
-        "metric": f"decode tok/s (batch {args.batch}, 2,048-token prompts, {shape_name})",
+        "metric": f"decode tok/s (batch {args.batch}, {prompt_len:,}-token prompts, {shape_name})",
         "value": main_point["tokens_per_s"],
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -349,8 +359,8 @@ def main() -> int:
             "vocab": config.vocab_size,
             "tied_head": config.tie_word_embeddings,
             "global_batch": args.batch,
-            "seq_len": CONTEXT,
-            "prompt_len": PROMPT,
+            "seq_len": context,
+            "prompt_len": prompt_len,
             "page_size": PAGE,
             "parallelism": "single GPU",
             "cuda_graphs": not args.no_graphs,

@@ -30,6 +30,12 @@ constexpr int kTileKeys = 64;
 constexpr int kWarps = 4;
 constexpr int kFlashThreads = kWarps * 32;
 constexpr int kMaxClusterSplits = 16;  // splits that may merge on chip: the widest cluster
+
+// An engine built for long requests cuts the key range more than 16 ways (the split count is
+// fixed when a decode step is captured, for the longest request allowed). A short request then
+// gives each split at least two 64-key tiles and leaves the other splits empty, which is how
+// it would have been cut with 16.
+__device__ __forceinline__ int min_tiles_per_split(int splits) { return splits > kMaxClusterSplits ? 2 : 1; }
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct FlashParams {
@@ -342,7 +348,7 @@ paged_flash_attention_kernel(const FlashParams p) {
   int tile_begin = lo / kTileKeys, tile_end = hi / kTileKeys + 1;
   if (DECODE && p.splits > 1) {
     const int tiles = tile_end - tile_begin;
-    const int per_split = (tiles + p.splits - 1) / p.splits;
+    const int per_split = max(min_tiles_per_split(p.splits), (tiles + p.splits - 1) / p.splits);
     tile_begin = tile_begin + split * per_split;
     tile_end = min(tile_end, tile_begin + per_split);
   }
@@ -534,30 +540,42 @@ paged_flash_attention_kernel(const FlashParams p) {
 }
 
 // out[row, :] = sum_i partial_out[row, i, :] * 2^(m_i - M) / sum_i l_i * 2^(m_i - M), one block
-// per (token, query head) row (python/instinct/backends/metal_kernels.py:103-124).
+// per (token, query head) row (python/instinct/backends/metal_kernels.py:103-124). The block
+// is [head dims, groups]: group g takes splits 16 g .. 16 g + 15, so up to 64 splits cost one
+// round trip to L2 and one pass through shared memory; a block of one group loops over more.
+constexpr int kMergeGroups = 4;
+
+__host__ __device__ constexpr int merge_groups(int splits) {
+  return splits <= kMaxClusterSplits * kMergeGroups ? (splits + kMaxClusterSplits - 1) / kMaxClusterSplits : 1;
+}
+
 template <int HEAD_DIM>
 __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
                                    const float* __restrict__ partial_ml,
                                    __nv_bfloat16* __restrict__ out, int splits) {
+  __shared__ float group_acc[kMergeGroups][HEAD_DIM];
+  __shared__ float2 group_ml[kMergeGroups];
   let_successor_start();
   wait_for_predecessor();
   const int64_t row = blockIdx.x;
   const float2* ml = reinterpret_cast<const float2*>(partial_ml + row * splits * 2);
-  if (splits <= kMaxClusterSplits && HEAD_DIM <= static_cast<int>(blockDim.x)) {
-    // Every load of this thread (the splits' maxima and sums, and its dim of every split's
-    // output) is requested before the first is used: one round trip to L2 instead of three.
-    const int d = threadIdx.x;
+  const int groups = static_cast<int>(blockDim.y);
+  if (splits <= kMaxClusterSplits * groups && HEAD_DIM <= static_cast<int>(blockDim.x)) {
+    // Every load of this thread (its splits' maxima and sums, and its dim of each of their
+    // outputs) is requested before the first is used: one round trip to L2 instead of three.
+    const int d = threadIdx.x, g = threadIdx.y, base = g * kMaxClusterSplits;
     float2 stats[kMaxClusterSplits];
     float values[kMaxClusterSplits];
 #pragma unroll
     for (int i = 0; i < kMaxClusterSplits; ++i) {
-      stats[i] = i < splits ? ml[i] : make_float2(-INFINITY, 0.f);
-      values[i] = i < splits && d < HEAD_DIM ? partial_out[(row * splits + i) * HEAD_DIM + d] : 0.f;
+      const bool live = base + i < splits;
+      stats[i] = live ? ml[base + i] : make_float2(-INFINITY, 0.f);
+      values[i] = live && d < HEAD_DIM ? partial_out[(row * splits + base + i) * HEAD_DIM + d] : 0.f;
     }
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < kMaxClusterSplits; ++i) m = fmaxf(m, stats[i].x);
-    const float use = m == -INFINITY ? 0.f : m;
+    float use = m == -INFINITY ? 0.f : m;
     float l = 0.f, acc = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxClusterSplits; ++i) {
@@ -565,9 +583,26 @@ __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
       l += stats[i].y * f;
       acc += values[i] * f;
     }
+    if (groups > 1) {
+      // The groups' results meet in shared memory and are added in group order.
+      if (d < HEAD_DIM) group_acc[g][d] = acc;
+      if (d == 0) group_ml[g] = make_float2(m, l);
+      __syncthreads();
+      if (g != 0) return;
+      m = -INFINITY;
+      for (int j = 0; j < groups; ++j) m = fmaxf(m, group_ml[j].x);
+      use = m == -INFINITY ? 0.f : m;
+      l = 0.f, acc = 0.f;
+      for (int j = 0; j < groups; ++j) {
+        const float f = exp2f(group_ml[j].x - use);
+        l += group_ml[j].y * f;
+        if (d < HEAD_DIM) acc += group_acc[j][d] * f;
+      }
+    }
     if (d < HEAD_DIM) out[row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     return;
   }
+  if (threadIdx.y != 0) return;
   float m = -INFINITY;
 #pragma unroll 8
   for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i].x);
@@ -665,7 +700,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   int tile_begin = lo / kTileKeys, tile_end = hi / kTileKeys + 1;
   if (p.splits > 1) {
     const int tiles = tile_end - tile_begin;
-    const int per_split = (tiles + p.splits - 1) / p.splits;
+    const int per_split = max(min_tiles_per_split(p.splits), (tiles + p.splits - 1) / p.splits);
     tile_begin = tile_begin + split * per_split;
     tile_end = min(tile_end, tile_begin + per_split);
   }
@@ -910,8 +945,9 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
     }
     launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
-      launch_kernel(flash_merge_kernel<HEAD_DIM>, dim3(tokens * p.q_heads), dim3(HEAD_DIM <= 64 ? 64 : 128), 0,
-                    stream, p.partial_out, p.partial_ml, p.out, p.splits);
+      launch_kernel(flash_merge_kernel<HEAD_DIM>, dim3(tokens * p.q_heads),
+                    dim3(HEAD_DIM <= 64 ? 64 : 128, merge_groups(p.splits)), 0, stream, p.partial_out, p.partial_ml,
+                    p.out, p.splits);
     }
   } else {
     const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
@@ -1122,8 +1158,8 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   }
   if (status != cudaSuccess) return b200_fail("decode attention (TMA): %s", cudaGetErrorString(status));
   if (splits > 1 && !p.cluster_merge) {
-    status = launch_kernel(flash_merge_kernel<kTmaDim>, dim3(num_seqs * q_heads), dim3(128), 0, stream, p.partial_out,
-                           p.partial_ml, p.out, splits);
+    status = launch_kernel(flash_merge_kernel<kTmaDim>, dim3(num_seqs * q_heads), dim3(128, merge_groups(splits)), 0,
+                           stream, p.partial_out, p.partial_ml, p.out, splits);
     if (status != cudaSuccess) return b200_fail("decode attention (TMA) merge: %s", cudaGetErrorString(status));
   }
   return b200_check_launch("paged_decode_attention_tma");

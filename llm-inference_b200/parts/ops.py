@@ -295,6 +295,7 @@ def paged_attention_plain(
 
 NUM_SMS = 148
 DECODE_STAGES = 3  # pieces in flight per warp of the TMA decode kernel
+MAX_DECODE_SPLITS = 64  # what the merge kernel takes in one round trip
 
 
 def flash_attention_supported(ctx: StepContext, q_heads: int, kv_heads: int, head_dim: int, page_size: int, decode: bool) -> bool:
@@ -318,11 +319,16 @@ def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = Fal
     kernel (three blocks per SM) wants about two waves of blocks. The TMA kernel (rings three
     deep, two blocks per SM) wants all its blocks resident at once: measured on a B200 at
     2,048 keys, 64 requests x 2 kv heads take 26 us in 2 splits and 35 us in 6, and 64 x 8
-    take 82 us unsplit."""
+    take 82 us unsplit. Normally at most 16 splits. Very few pairs with many keys go up to 64
+    while every split keeps four tiles: one request of the 1.5B shape with 30,000 keys is 32
+    blocks for 148 SMs in 16 splits (1.94 ms per step) and 128 blocks in 64 (1.35 ms); 8,192
+    keys: 1.36 -> 1.15 ms. With 8 such requests 18 splits were no faster than 16 (2.26 vs
+    2.17 ms): the wider merge costs what the two extra splits gain."""
     tiles = max(1, (max_kv_len + 63) // 64)
     pairs = max(1, num_seqs * kv_heads)
     want = (2 if tma else 6) * NUM_SMS // pairs  # rounded down: one block too many would start another wave
-    return max(1, min(tiles, 16, want))
+    most = 16 if want < 32 else max(16, min(MAX_DECODE_SPLITS, tiles // 4))
+    return max(1, min(tiles, most, want))
 
 
 def paged_flash_attention(

@@ -466,8 +466,9 @@ def test_paged_flash_attention(lib, case):
         lead += 1
     if lead and ops.flash_attention_supported(ctx, q_heads, kv_heads, head_dim, page, True):
         # One block per request; splits merged on chip by a cluster (3, 8, 16 blocks) or through
-        # scratch memory by a second kernel (3, 40).
-        for splits, merge in ((1, "cluster"), (3, "cluster"), (8, "cluster"), (16, "cluster"), (3, "scratch"), (40, "scratch")):
+        # scratch memory by a second kernel (3; 40 and 64: its groups of 16 splits; 100: its loop).
+        for splits, merge in ((1, "cluster"), (3, "cluster"), (8, "cluster"), (16, "cluster"), (3, "scratch"), (40, "scratch"),
+                              (64, "scratch"), (100, "scratch")):
             ctx.options["attention_merge"] = merge
             out3 = torch.full_like(q, float("nan"))
             ops.paged_flash_attention(ctx, view, q, out3, q_heads, kv_heads, head_dim, head_dim**-0.5,
@@ -483,6 +484,7 @@ TMA_DECODE_CASES = [
     (40, 8, 64, 100, [333, 90, 99, 100, 1500]),
     (16, 1, 256, 70, [700, 69, 70, 2]),
     (3, 3, 64, 0, [129, 4000]),
+    (12, 2, 64, 0, [9000, 40, 2100]),  # a long request beside short ones, whose splits are mostly empty
 ]
 
 
@@ -505,8 +507,8 @@ def test_decode_attention_with_tma_loads(lib, case):
         view = CacheView(0, True, keys, values, torch.from_numpy(tables).cuda(), num_pages, tables.shape[1], page, window)
         # Splits merged through scratch memory by a second kernel, or on chip by a cluster.
         for splits, stages, merge in ((1, 2, "scratch"), (1, 6, "scratch"), (3, 2, "scratch"), (3, 3, "scratch"),
-                                      (7, 4, "scratch"), (40, 2, "scratch"), (2, 3, "cluster"), (8, 2, "cluster"),
-                                      (16, 3, "cluster")):
+                                      (7, 4, "scratch"), (40, 2, "scratch"), (64, 3, "scratch"), (100, 2, "scratch"),
+                                      (2, 3, "cluster"), (8, 2, "cluster"), (16, 3, "cluster")):
             ctx.options["decode_stages"] = stages
             ctx.options["attention_merge"] = merge
             out = torch.full_like(q, float("nan"))
