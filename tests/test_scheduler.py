@@ -254,3 +254,88 @@ def test_repeats_stops_before_the_context_limit():
     assert not s.repeats(plan)
     events = s.commit(plan, [9])
     assert events[0].finished and not s.has_work()
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_traffic_keeps_every_promise(seed):
+    """Random submits, cancels (also between plan and commit) and stop tokens over a full and a
+    window group with few pages: every plan keeps the budget, the portion sizes and the order;
+    requests start first come, first served; nothing stalls; every page and slot comes back."""
+    import numpy as np
+
+    rng = np.random.default_rng(100 + seed)
+    h = host()
+    page = int(rng.choice([2, 4, 8]))
+    window = int(rng.choice([0, 5, 12]))
+    seqs = int(rng.integers(1, 5))
+    chunk = int(rng.integers(1, 6))
+    burst = chunk + int(rng.integers(0, 6))
+    budget = seqs + int(rng.integers(0, 9))
+    context, vocab = 48, 20
+    full_pages = (context + page - 1) // page + int(rng.integers(0, 8))  # the longest request fits, little more
+    groups = [h.GroupSpec("full", full_pages, 0)]
+    if window:
+        groups.append(h.GroupSpec("window", (window + burst + page - 1) // page + 1 + int(rng.integers(0, 4)), window))
+    cache = h.CacheManager(page, groups, seqs, burst)
+    s = h.Scheduler(cache, seqs, context, budget, chunk, burst, vocab, 1)
+
+    submitted, first_seen, cancelled_waiting, stops = [], [], set(), {}
+    steps = 0
+    while steps < 400 and (steps < 120 or s.has_work()):
+        steps += 1
+        if steps < 120 and rng.random() < 0.5:
+            prompt = [int(t) for t in rng.integers(0, vocab, int(rng.integers(1, 31)))]
+            new = int(rng.integers(1, min(12, context - len(prompt)) + 1))
+            stop = [int(rng.integers(0, vocab))] if rng.random() < 0.4 else []
+            rid = s.submit(prompt, new, stop, h.SamplingParams())
+            submitted.append(rid)
+            stops[rid] = set(stop)
+        live = [r for r in submitted if s.request(r).state in ("waiting", "prefilling", "running")]
+        if live and rng.random() < 0.1:
+            victim = int(rng.choice(live))
+            if s.request(victim).state == "waiting":
+                cancelled_waiting.add(victim)
+            s.cancel(victim)
+        if not s.has_work():
+            continue
+        plan = s.plan()
+        entries = plan.entries
+        assert entries, "work is waiting but the plan is empty"
+        assert plan.total_tokens <= budget and len(entries) <= seqs
+        assert len({e.request_id for e in entries}) == len(entries)
+        kinds = [e.decode for e in entries]
+        assert kinds == sorted(kinds, reverse=True), "single decoded tokens come first"
+        portion = chunk if any(kinds) else burst
+        for e in entries:
+            request = s.request(e.request_id)
+            assert e.start == cache.length(e.request_id) == request.length
+            if e.decode:
+                assert e.count == 1 and e.wants_token and request.state == "running"
+            else:
+                assert 1 <= e.count <= portion and request.state == "prefilling"
+                assert e.wants_token == (e.start + e.count == len(request.prompt))
+            if e.request_id not in first_seen:
+                first_seen.append(e.request_id)
+        cache.check_invariants()
+        if rng.random() < 0.1:  # a cancel while the step runs
+            s.cancel(int(rng.choice([e.request_id for e in entries])))
+        events = s.commit(plan, [int(rng.integers(0, vocab)) for e in entries if e.wants_token])
+        cache.check_invariants()
+        for event in events:
+            request = s.request(event.request_id)
+            assert len(request.output) <= request.max_new_tokens
+            if event.finished:
+                assert request.state == "completed" and not cache.contains(event.request_id)
+                assert (event.reason == "stop") == (event.token in stops[event.request_id])
+                assert event.reason != "length" or len(request.output) == request.max_new_tokens
+    assert not s.has_work(), "requests were left over"
+    assert first_seen == [r for r in submitted if r in set(first_seen)], "requests started out of order"
+    never_started = [r for r in submitted if r not in set(first_seen)]
+    assert all(r in cancelled_waiting for r in never_started)
+    assert all(s.request(r).state in ("completed", "cancelled") for r in submitted)
+    stats = cache.stats()
+    for pool in stats["kv_pools"].values():
+        assert pool["used_pages"] == 0 and pool["reserved_pages"] == 0
+    assert stats["free_state_slots"] == seqs and stats["requests"] == 0
+    totals = s.stats()
+    assert totals["submitted"] == len(submitted) and totals["completed"] + totals["cancelled"] == len(submitted)
