@@ -169,8 +169,19 @@ def peak_tokens(steps) -> int:
 
 
 # Sizes far from the two tiny configurations: many heads over a narrow width with wide heads
-# (the output projection's inner size is a hundred times its outer one), and the smallest heads.
+# (the output projection's inner size is a hundred times its outer one), the smallest heads, and
+# heads of 128 and 64, which in bfloat16 run the tensor-core attention kernels (prompt portions
+# on tcgen05 or mma.sync, single tokens on the split-key kernels fed by TMA or cp.async) where
+# the others run the plain kernel; one of them with a window that ends inside a page.
 OTHER_SIZES = {
+    "heads_of_128": dict(
+        TINY["B"], hidden_size=136, head_dim=128, num_attention_heads=6, num_key_value_heads=2, intermediate_size=200,
+        vocab_size=401, num_hidden_layers=2, sliding_window=70, max_window_layers=1, max_position_embeddings=512,
+    ),
+    "heads_of_64": dict(
+        TINY["A"], hidden_size=88, head_dim=64, num_attention_heads=5, num_key_value_heads=5, intermediate_size=120,
+        vocab_size=333, num_hidden_layers=2, max_position_embeddings=512,
+    ),
     "wide_heads": dict(
         TINY["B"], hidden_size=40, head_dim=192, num_attention_heads=21, num_key_value_heads=3, intermediate_size=520,
         vocab_size=257, num_hidden_layers=2, sliding_window=17, max_window_layers=1, rms_norm_eps=3e-6,
