@@ -178,7 +178,11 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
     prompt_len = args.prompt_len
-    context = args.context or max(CONTEXT, 2 * prompt_len)
+    steps, warmup = args.steps, args.warmup
+    new_tokens = max(256, steps + warmup + 1)  # every request decodes through the timed steps
+    # The engine is built for twice the prompt (the headline run: 2,048 in 4,096) or for what
+    # the timed steps need, whichever is longer.
+    context = args.context or max(CONTEXT, 2 * prompt_len, -(-(prompt_len + new_tokens) // PAGE) * PAGE)
 
     import numpy as np
     import torch
@@ -204,16 +208,14 @@ def main() -> int:
     shape_name = args.model.replace("qwen", "Qwen").replace("b", "B") + " shape"
     raw = dict(shape, num_hidden_layers=args.layers, max_window_layers=args.layers)
     _, config = parse_config(raw)
-    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
-    max_batch = max(64, args.batch)
-    steps, warmup = args.steps, args.warmup
-    new_tokens = 256
-    if steps + warmup + 1 > new_tokens:
-        new_tokens = steps + warmup + 1
+    if not args.context:
+        context = min(context, config.max_position_embeddings)
     if prompt_len < 1 or context < max(PROMPT, prompt_len + new_tokens) or context > config.max_position_embeddings:
         print(f"bench.py: --context {context} must hold the {PROMPT}-token prefill and {prompt_len} + {new_tokens} tokens "
               f"of each request, within the model's {config.max_position_embeddings} positions")
         return 2
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    max_batch = max(64, args.batch)
     budget_tokens = max_batch * (prompt_len + new_tokens + PAGE)
     kv_bytes_per_token = 2 * args.layers * config.num_key_value_heads * config.head_dim * 2
     engine = Engine(
