@@ -86,3 +86,24 @@ def test_sampling_filters():
     sharp = plain.surviving_probabilities(logits, 0.5)
     assert np.allclose(sharp, np.array([0.25, 0.04, 0.04, 0.0036, 0.0016]) / 0.3352)
     assert plain.draw_key(3, 2) == 3_000_011 and 0.0 <= plain.uniform_from_key(5) < 1.0
+
+
+def test_how_decode_attention_cuts_the_key_range():
+    """The split rule is a pure function of the batch and the longest request: never more
+    splits than 64-key tiles, 16 at most at ordinary lengths, up to 64 only for very few
+    (request, kv head) pairs with many keys, and no split once the batch fills the GPU."""
+    from llm_inference_b200.parts.ops import MAX_DECODE_SPLITS, decode_splits
+
+    for tma in (False, True):
+        for seqs in (1, 2, 8, 64, 300):
+            for kv_heads in (1, 2, 8):
+                for keys in (1, 64, 65, 1000, 4096, 32768, 131072):
+                    splits = decode_splits(seqs, kv_heads, keys, tma)
+                    assert 1 <= splits <= min(MAX_DECODE_SPLITS, (keys + 63) // 64)
+                    if keys <= 4096:
+                        assert splits <= 16
+    assert decode_splits(1, 2, 4096, True) == 16 and decode_splits(8, 2, 4096, True) == 16
+    assert decode_splits(1, 2, 32768, True) == 64 and decode_splits(8, 2, 32768, True) == 16
+    assert decode_splits(1, 8, 32768, True) == 37  # 296 resident blocks / 8 pairs
+    assert decode_splits(64, 2, 2048, True) == 2 and decode_splits(64, 8, 2048, True) == 1
+    assert decode_splits(1, 2, 100, True) == 2
