@@ -68,3 +68,26 @@ def test_benchmark_with_a_random_shape_and_a_synthetic_mix(tmp_path):
     assert report["configuration"]["model_path"] == "random:tiny-b"
     neither = run("benchmark", "--mix", "2", "--output", str(result), check=False)
     assert neither.returncode != 0 and "--model DIR or --random SHAPE" in neither.stderr
+
+
+def test_replay_checks_its_options_and_needs_a_gpu(tmp_path):
+    """Options are checked before anything is loaded; without a CUDA device the tool says so
+    and exits (there is no CPU path to fall back to)."""
+    import torch
+
+    from helpers import TRACE_RUN
+
+    folder = tmp_path / "tiny"
+    run("random_model", "--preset", "tiny-a", "--seed", "2", "--out", str(folder))
+    base = [sys.executable, str(TRACE_RUN), "--model", str(folder), "--dtype", "float32", "--out", str(tmp_path / "out")]
+    step = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1, 2], "want": [1]}], "end": ["a"]}) + "\n"
+    for extra, message in (
+        (["--max-tokens", "0"], "--max-tokens must be positive"),
+        (["--max-tokens", "64", "--page-size", "48"], "--page-size must divide 64"),
+        (["--max-tokens", "64", "--dtype", "float16"], "invalid choice"),
+    ):
+        bad = subprocess.run(base + extra, input=step, capture_output=True, text=True, timeout=300)
+        assert bad.returncode == 2 and message in bad.stderr
+    if not torch.cuda.is_available():
+        result = subprocess.run(base + ["--max-tokens", "64"], input=step, capture_output=True, text=True, timeout=300)
+        assert result.returncode == 2 and "no CUDA device" in result.stderr and "done" not in result.stdout
