@@ -62,17 +62,26 @@ class SafetensorsFile:
                 header = json.loads(self._file.read(header_len))
             except (json.JSONDecodeError, UnicodeDecodeError) as exc:
                 raise SafetensorsError(f"{self.path}: header is not JSON: {exc}") from exc
+            if not isinstance(header, dict):
+                raise SafetensorsError(f"{self.path}: header is not a JSON object")
             self._data_start = 8 + header_len
             self.metadata = header.pop("__metadata__", {}) or {}
             self.tensors: dict[str, TensorInfo] = {}
             for name, entry in header.items():
+                if not isinstance(entry, dict):
+                    raise SafetensorsError(f"{self.path}: the entry of tensor '{name}' is not an object")
                 dtype = _DTYPES.get(entry.get("dtype"))
                 if dtype is None:
                     raise SafetensorsError(
                         f"{self.path}: tensor '{name}' has unsupported dtype {entry.get('dtype')!r}"
                     )
-                shape = tuple(int(s) for s in entry["shape"])
-                begin, end = (int(v) for v in entry["data_offsets"])
+                try:
+                    shape = tuple(int(s) for s in entry["shape"])
+                    begin, end = (int(v) for v in entry["data_offsets"])
+                except (KeyError, TypeError, ValueError) as exc:
+                    raise SafetensorsError(f"{self.path}: tensor '{name}' has no usable shape and data_offsets") from exc
+                if any(s < 0 for s in shape):
+                    raise SafetensorsError(f"{self.path}: tensor '{name}' has a negative size")
                 count = 1
                 for s in shape:
                     count *= s
@@ -114,7 +123,7 @@ class SafetensorsFile:
 def write_safetensors(
     path: str | Path, tensors: dict[str, torch.Tensor], metadata: dict[str, str] | None = None
 ) -> None:
-    """Write ``tensors`` in name order; each starts at an 8-byte-aligned offset."""
+    """Write ``tensors`` in name order, back to back; the data section starts 8-byte aligned."""
     header: dict[str, object] = {}
     if metadata:
         header["__metadata__"] = dict(metadata)

@@ -168,3 +168,55 @@ def test_run_order_is_data():
     recipe.schedule = [LayerCall(0), LayerCall(2, cache=1, writes=False)]
     with pytest.raises(ValueError, match="nobody writes"):
         Model(recipe).cache_specs()
+
+
+def test_safetensors_round_trip_and_malformed_files(tmp_path):
+    """Whatever the writer writes the reader returns bit for bit (odd sizes, empty tensors,
+    every stored dtype); a damaged container is refused with one kind of error that names
+    the file."""
+    import struct
+
+    import numpy as np
+    import torch
+
+    from llm_inference_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
+
+    rng = np.random.default_rng(3)
+    tensors = {
+        "a.weight": torch.from_numpy(rng.standard_normal((3, 5)).astype(np.float32)),
+        "b.odd": torch.from_numpy(rng.standard_normal(7).astype(np.float32)).to(torch.bfloat16),
+        "c.half": torch.from_numpy(rng.standard_normal((2, 1, 3)).astype(np.float16)),
+        "d.table": torch.from_numpy(rng.integers(-5, 5, (4, 2))).to(torch.int64),
+        "e.empty": torch.empty(0, 4),
+        "f.scalar": torch.tensor(2.5),
+        "g.bytes": torch.arange(11, dtype=torch.uint8),
+    }
+    path = tmp_path / "model.safetensors"
+    write_safetensors(path, tensors, metadata={"format": "pt"})
+    with SafetensorsFile(path) as file:
+        assert file.metadata == {"format": "pt"} and set(file.tensors) == set(tensors)
+        for name, tensor in tensors.items():
+            got = file.read(name)
+            assert got.dtype == tensor.dtype and got.shape == tensor.shape
+            assert got.reshape(-1).view(torch.uint8).tolist() == tensor.contiguous().reshape(-1).view(torch.uint8).tolist()
+
+    def container(header: bytes, data: bytes = b"") -> None:
+        path.write_bytes(struct.pack("<Q", len(header)) + header + data)
+
+    damaged = {
+        "too short": lambda: path.write_bytes(b"\x01\x02"),
+        "header length exceeds": lambda: path.write_bytes(struct.pack("<Q", 1 << 40) + b"{}"),
+        "not JSON": lambda: container(b"{ nope"),
+        "not a JSON object": lambda: container(b"[1, 2]"),
+        "is not an object": lambda: container(json.dumps({"w": 3}).encode()),
+        "unsupported dtype": lambda: container(json.dumps({"w": {"dtype": "F8_E4M3", "shape": [1], "data_offsets": [0, 1]}}).encode(), b"\0"),
+        "no usable shape": lambda: container(json.dumps({"w": {"dtype": "F32", "data_offsets": [0, 4]}}).encode(), b"\0" * 4),
+        "negative size": lambda: container(json.dumps({"w": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 4]}}).encode(), b"\0" * 4),
+        "bad byte range": lambda: container(json.dumps({"w": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}).encode(), b"\0" * 8),
+        "runs past the file": lambda: container(json.dumps({"w": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}).encode(), b"\0" * 4),
+    }
+    for message, damage in damaged.items():
+        damage()
+        with pytest.raises(SafetensorsError, match=message) as caught:
+            SafetensorsFile(path)
+        assert str(path) in str(caught.value)
