@@ -134,15 +134,19 @@ class Qwen2Config(ModelConfig):
         # (python/instinct/format.py:88-101).
         rope_theta = raw.get("rope_theta")
         if rope_theta is None:
-            rope_theta = (raw.get("rope_parameters") or {}).get("rope_theta")
+            parameters = raw.get("rope_parameters")
+            rope_theta = parameters.get("rope_theta") if isinstance(parameters, dict) else None
         if rope_theta is None:
             raise ConfigError("config.json is missing required key 'rope_theta'")
-        scaling = raw.get("rope_scaling")
-        if scaling not in (None, {}) and (scaling.get("rope_type") or scaling.get("type")) not in (
-            None,
-            "default",
-        ):
-            raise ConfigError(f"rope_scaling {scaling!r} is not supported (only plain RoPE)")
+        # Scaled variants may sit under either key; both are refused rather than run unscaled.
+        for key in ("rope_scaling", "rope_parameters"):
+            scaling = raw.get(key)
+            if scaling in (None, {}):
+                continue
+            if not isinstance(scaling, dict):
+                raise ConfigError(f"config.json key '{key}' must be an object, got {scaling!r}")
+            if (scaling.get("rope_type") or scaling.get("type")) not in (None, "default"):
+                raise ConfigError(f"{key} {scaling!r} is not supported (only plain RoPE)")
         hidden = _take(raw, "hidden_size", int)
         heads = _take(raw, "num_attention_heads", int)
         head_dim = _take(raw, "head_dim", int, 0)

@@ -61,6 +61,8 @@ def test_config_reads_every_size_from_json():
         ({"head_dim": 15}, "head_dim"),
         ({"use_sliding_window": True, "sliding_window": 0, "max_window_layers": 0}, "sliding_window"),
         ({"rope_scaling": {"rope_type": "yarn", "factor": 4}}, "rope_scaling"),
+        ({"rope_theta": None, "rope_parameters": {"rope_theta": 1e6, "rope_type": "yarn", "factor": 4}}, "rope_parameters"),
+        ({"rope_scaling": "linear"}, "must be an object"),
         ({"num_hidden_layers": "two"}, "must be an integer"),
     ],
 )
