@@ -19,6 +19,7 @@ def add_engine_options(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--model", type=Path, default=None, help="folder with config.json and *.safetensors")
     parser.add_argument("--random", default=None, metavar="SHAPE", help="instead of --model: a named shape (cli/presets.py) with seeded random weights drawn on the device")
     parser.add_argument("--weights-seed", type=int, default=0, help="seed of --random's weights")
+    parser.add_argument("--backend", choices=["auto", "cuda", "b200"], default="auto", help="kept from the reference's tools; this engine has one backend")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--max-sequences", type=int, default=16)
     parser.add_argument("--max-model-length", type=int, default=2048)
@@ -51,7 +52,7 @@ def engine_from(args):
             raise SystemExit(f"--random {args.random!r}: known shapes are {', '.join(sorted(PRESETS))}")
         _, config = parse_config(PRESETS[args.random])
         options["model"] = random_model(config, seed=args.weights_seed, dtype=args.dtype)
-    return create_engine(args.model, **options)
+    return create_engine(args.model, backend=args.backend, **options)
 
 
 def main(argv=None) -> int:
