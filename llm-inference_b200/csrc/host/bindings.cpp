@@ -113,6 +113,13 @@ PYBIND11_MODULE(b200_host, m) {
         return out;
       });
 
+  m.def("sampling_ranges", []() {
+    py::dict out;
+    for (const SamplingRange& r : sampling_ranges())
+      out[r.field] = py::make_tuple(r.low, r.high, r.low_open, r.high_open, r.whole);
+    return out;
+  });
+
   py::class_<SamplingParams>(m, "SamplingParams")
       .def(py::init([](double temperature, double top_p, int top_k, double min_p,
                        std::optional<std::int64_t> seed) {

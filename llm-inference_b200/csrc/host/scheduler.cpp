@@ -6,12 +6,31 @@
 
 namespace b200 {
 
+const std::vector<SamplingRange>& sampling_ranges() {
+  // The same table as sampling/params.py::RANGES; a test compares them.
+  static const std::vector<SamplingRange> table = {
+      {"temperature", 0.0, 10.0, false, false, false},
+      {"top_p", 0.0, 1.0, true, false, false},
+      {"top_k", 0.0, 2147483647.0, false, false, true},
+      {"min_p", 0.0, 1.0, false, true, false},
+  };
+  return table;
+}
+
 void SamplingParams::validate() const {
-  if (!(std::isfinite(temperature) && temperature >= 0.0 && temperature <= 10.0))
-    throw std::invalid_argument("temperature must be between 0 and 10");
-  if (!(top_p > 0.0 && top_p <= 1.0)) throw std::invalid_argument("top_p must be in (0, 1]");
-  if (top_k < 0) throw std::invalid_argument("top_k must be a non-negative integer");
-  if (!(min_p >= 0.0 && min_p < 1.0)) throw std::invalid_argument("min_p must be in [0, 1)");
+  const double values[] = {temperature, top_p, static_cast<double>(top_k), min_p};
+  std::string broken;
+  std::size_t i = 0;
+  for (const SamplingRange& r : sampling_ranges()) {
+    const double v = values[i++];
+    const bool above = r.low_open ? v > r.low : v >= r.low;
+    const bool below = r.high_open ? v < r.high : v <= r.high;
+    if (std::isfinite(v) && above && below) continue;
+    if (!broken.empty()) broken += "; ";
+    broken += std::string(r.field) + "=" + std::to_string(v) + " is outside " + (r.low_open ? "(" : "[") +
+              std::to_string(r.low) + ", " + std::to_string(r.high) + (r.high_open ? ")" : "]");
+  }
+  if (!broken.empty()) throw std::invalid_argument("sampling settings refused: " + broken);
 }
 
 Scheduler::Scheduler(CacheManager& cache, int max_num_sequences, int max_model_length,

@@ -26,6 +26,14 @@ namespace b200 {
 
 enum class SequenceState : std::uint8_t { waiting, prefilling, running, completed, cancelled, rejected };
 
+// One row of the table of allowed sampling settings (field, interval, whether whole numbers only).
+struct SamplingRange {
+  const char* field;
+  double low, high;
+  bool low_open, high_open, whole;
+};
+const std::vector<SamplingRange>& sampling_ranges();
+
 struct SamplingParams {
   double temperature{0.0};
   double top_p{1.0};

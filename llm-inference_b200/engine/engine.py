@@ -47,8 +47,9 @@ class TokenEvent:
     request_id: int
     token: int
     finished: bool
-    # "stop" (an end token), "length" (the request's token budget) or "context" (the
-    # model's context limit); empty while running.
+    # Set together with `finished`: "stop" when one of the request's stop tokens came out,
+    # "length" when max_new_tokens were produced, "context" when the next position would pass
+    # the engine's length limit.
     reason: str = ""
 
 

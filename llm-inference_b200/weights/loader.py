@@ -6,9 +6,14 @@ reads exactly those names from a folder's ``*.safetensors`` and raises one
 wrong shape (the reference checks names and shapes tensor by tensor:
 python/instinct/model_contract.py:10-78, src/qwen_validation.cpp:11-46).
 
-Stored 16-bit floats are kept as bfloat16, stored 32-bit floats stay 32-bit and
-integer tables become int32; which of these a kernel then computes in is the owning
-part's decision when it packs its weights.
+The loader changes no float's value: a tensor stored as float16, bfloat16 or float32 is handed
+over in that format (64-bit floats become float32, integer tables int32), and the owning
+part makes the one conversion to the dtype it computes in when it packs its weights. A
+float32 engine therefore computes with exactly the stored float16 values, as the reference
+widens its float16 tensors straight to the compute type
+(python/instinct/backends/dense.py:36-48, storage format python/instinct/format.py:204-207);
+for a bfloat16 engine rounding float16 to bfloat16 is the only possible choice, and it
+happens once, in the part.
 """
 
 from __future__ import annotations
@@ -81,8 +86,8 @@ def checkpoint_files(folder: str | Path) -> list[Path]:
 def _stored_to_kept(tensor: torch.Tensor, spec: TensorSpec) -> torch.Tensor:
     if spec.integer:
         return tensor.to(torch.int32)
-    if tensor.dtype in (torch.float16, torch.bfloat16):
-        return tensor.to(torch.bfloat16)
+    if tensor.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        return tensor
     return tensor.to(torch.float32)
 
 

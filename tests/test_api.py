@@ -29,6 +29,18 @@ def test_sampling_parameters_are_validated(bad):
         SamplingParams(**bad)
 
 
+def test_python_and_scheduler_hold_the_same_sampling_ranges():
+    from llm_inference_b200.csrc.host_module import host
+    from llm_inference_b200.sampling.params import RANGES
+
+    native = host().sampling_ranges()
+    assert {name: tuple(r) for name, r in RANGES.items()} == {name: tuple(r) for name, r in native.items()}
+    with pytest.raises(ValueError, match="top_p"):
+        host().SamplingParams(0.5, 0.0, 0, 0.0, None)
+    with pytest.raises(ValueError, match="temperature.*min_p"):
+        SamplingParams(temperature=11.0, min_p=1.0)
+
+
 def test_sampling_defaults_and_greedy():
     assert SamplingParams() == SamplingParams(temperature=0.0, top_p=1.0, top_k=0, min_p=0.0, seed=None)
     assert SamplingParams().greedy and SamplingParams(temperature=0.8, top_k=1).greedy

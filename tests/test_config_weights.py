@@ -115,10 +115,34 @@ def test_loader_keeps_stored_precision(tmp_path):
         TensorSpec("absent", (2,), optional=True),
     ]
     loaded = load_weights(tmp_path, specs)
-    assert loaded["half"].dtype == torch.bfloat16 and loaded["brain"].dtype == torch.bfloat16
+    assert loaded["half"].dtype == torch.float16 and torch.equal(loaded["half"], tensors["half"])
+    assert loaded["brain"].dtype == torch.bfloat16 and torch.equal(loaded["brain"], tensors["brain"])
     assert loaded["single"].dtype == torch.float32 and torch.equal(loaded["single"], tensors["single"])
     assert loaded["table"].dtype == torch.int32 and loaded["table"].tolist() == list(range(6))
     assert "absent" not in loaded
+
+
+def test_float16_checkpoint_reaches_a_float32_model_unrounded(tmp_path):
+    """A float32 model computes with exactly the stored float16 values; a bfloat16 model
+    rounds them once."""
+    folder = make_model_folder(tmp_path / "m", TINY_A, seed=4)
+    with SafetensorsFile(folder / "model.safetensors") as file:
+        tensors = {name: file.read(name) for name in file.tensors}
+    generator = torch.Generator().manual_seed(0)
+    halves = {
+        name: (torch.randn(t.shape, generator=generator) * 0.02 + (1.0 if name.endswith("norm.weight") else 0.0)).to(torch.float16)
+        for name, t in tensors.items()
+    }
+    write_safetensors(folder / "model.safetensors", halves)
+    model = load_model(folder, "float32", "cpu")
+    down = model.blocks[1].feed_forward.w_down
+    assert down.dtype == torch.float32 and torch.equal(down, halves["model.layers.1.mlp.down_proj.weight"].float())
+    assert torch.equal(model.embedding.table, halves["model.embed_tokens.weight"].float())
+    assert torch.equal(model.final_norm.weight, halves["model.norm.weight"].float())
+    # float16 keeps three more mantissa bits than bfloat16: most of these values would change.
+    assert not torch.equal(down, down.to(torch.bfloat16).float())
+    rounded = load_model(folder, "bfloat16", "cpu")
+    assert torch.equal(rounded.blocks[1].feed_forward.w_down, halves["model.layers.1.mlp.down_proj.weight"].to(torch.bfloat16))
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):

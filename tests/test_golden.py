@@ -62,8 +62,11 @@ def test_engine_matches_the_reference_outputs(golden, name, tmp_path):
     config = dict(maker.plain_config(case), architectures=["Qwen2ForCausalLM"], model_type="qwen2",
                   max_position_embeddings=128, eos_token_id=2)
     (tmp_path / "config.json").write_text(json.dumps(config))
-    # Stored in 32-bit so the float16-exact values reach the engine unchanged.
-    write_safetensors(tmp_path / "model.safetensors", {k: torch.from_numpy(v.astype(np.float32)) for k, v in tensors.items()})
+    # Stored in float16, the reference's own storage format (python/instinct/format.py:204-207):
+    # the float32 engine must compute with these values unrounded.
+    stored = {k: torch.from_numpy(v.astype(np.float16)) for k, v in tensors.items()}
+    assert all(np.array_equal(stored[k].numpy().astype(v.dtype), v) for k, v in tensors.items()), "weights are float16-exact"
+    write_safetensors(tmp_path / "model.safetensors", stored)
     prompts = maker.prompts_for(case)
     with create_engine(tmp_path, dtype="float32", max_num_sequences=3, kv_cache_bytes=1 << 20, prefill_chunk_size=5,
                        prefill_burst_size=8, page_size=4) as engine:
