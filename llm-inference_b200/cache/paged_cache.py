@@ -130,7 +130,8 @@ class PagedCache:
         self.state_slots = max_num_sequences if self.state_specs else 0
         self.states: dict[int, list[torch.Tensor]] = {
             cache_id: [
-                torch.zeros((self.state_slots, *shape), dtype=dt, device=self.device)
+                # One slot more than requests: the target of the padding rows of a captured step.
+                torch.zeros((self.state_slots + 1, *shape), dtype=dt, device=self.device)
                 for shape, dt in zip(spec.shapes, spec.dtypes)
             ]
             for cache_id, spec in self.state_specs.items()
@@ -166,6 +167,10 @@ class PagedCache:
 
     def null_page(self, group: CacheGroup) -> int:
         return group.capacity_pages
+
+    def null_slot(self) -> int:
+        """The state slot no request holds (padding rows write there); -1 without state."""
+        return self.state_slots if self.state_specs else -1
 
     # -- what a step needs ----------------------------------------------------------------------
 

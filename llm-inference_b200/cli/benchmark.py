@@ -24,21 +24,30 @@ import json
 import math
 import sys
 import time
+
+import numpy as np
 from pathlib import Path
 
 from .generate import add_engine_options, engine_from
 
 
 def percentiles(values: list[float]) -> dict[str, float]:
-    """p50 / p95 / p99 by the nearest-rank rule (python/instinct/benchmark.py:94-107)."""
-    if not values:
-        return {"p50": 0.0, "p95": 0.0, "p99": 0.0}
-    ordered = sorted(values)
+    """p50 / p95 / p99, each interpolated linearly between the two samples around rank
+    ``q * (n - 1)``: the rule the reference's benchmark reports with
+    (python/instinct/benchmark.py:94-107), so that the same samples give the same figures.
+    Empty input gives NaN, as there."""
+    ranked = np.sort(np.asarray(values, dtype=np.float64))
 
-    def pick(q: float) -> float:
-        return ordered[min(len(ordered) - 1, max(0, math.ceil(q * len(ordered)) - 1))]
+    def at(q: float) -> float:
+        if ranked.size == 0:
+            return math.nan
+        rank = q * (ranked.size - 1)
+        below = int(rank)
+        above = min(below + 1, ranked.size - 1)
+        share = rank - below
+        return float(ranked[below] + (ranked[above] - ranked[below]) * share)
 
-    return {"p50": pick(0.50), "p95": pick(0.95), "p99": pick(0.99)}
+    return {"p50": at(0.50), "p95": at(0.95), "p99": at(0.99)}
 
 
 def synthetic_mix(count: int, prompt_lengths, output_lengths, vocab: int, seed: int):

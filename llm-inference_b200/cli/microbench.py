@@ -98,6 +98,8 @@ def bench_gemm(args) -> dict:
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") / k**0.5).to(torch.bfloat16)
     ctx = make_ctx(positions=[0] * m, options={"gemm": args.gemm})
+    if args.plan is not None:
+        ctx.lib.lib.b200_stream_gemm_plan_override(*args.plan)
     if args.rotate:
         # Enough copies of the weights that one round exceeds the L2 cache several times.
         copies = max(2, -(-(512 << 20) // (w.numel() * 2)))
@@ -192,6 +194,8 @@ def main(argv=None) -> int:
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
     parser.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "skinny", "library"])
     parser.add_argument("--rotate", action="store_true", help="launch back to back over rotating copies of the weights")
+    parser.add_argument("--plan", type=int, nargs=3, metavar=("STAGES", "BLOCKS", "CLUSTER"), default=None,
+                        help="tcgen05 product: force ring depth, blocks aimed at and cluster width (0 = the planner's choice)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048)
     parser.add_argument("--tokens", type=int, default=2048)

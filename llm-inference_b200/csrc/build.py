@@ -205,35 +205,76 @@ def build_kernels(force: bool = False) -> Path:
     return out
 
 
-def host_module_path() -> Path:
+# The checked build of the host runtime: AddressSanitizer and UndefinedBehaviorSanitizer, as the
+# reference's CI runs its host C++ under them (.github/workflows/ci.yml:62-79). Python must then
+# start with the sanitizer's runtime preloaded: see `sanitizer_environment`.
+SANITIZE_FLAGS = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-O1", "-g"]
+
+
+def host_module_path(sanitize: bool = False) -> Path:
     suffix = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
-    return build_dir() / f"b200_host{suffix}"
+    folder = build_dir() / "sanitize" if sanitize else build_dir()
+    return folder / f"b200_host{suffix}"
 
 
-def build_host(force: bool = False) -> Path:
-    """Build (if stale) and return the path of the C++ host extension module."""
+def _sanitizing_compiler() -> tuple[str, str]:
+    """(compiler, its AddressSanitizer runtime): the first of $CXX, g++, c++ and /usr/bin/g++
+    that ships one."""
+    tried = []
+    for cxx in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), "/usr/bin/g++"):
+        if not cxx or cxx in tried or not Path(cxx).exists():
+            continue
+        tried.append(cxx)
+        runtime = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+        if runtime and Path(runtime).is_absolute() and Path(runtime).exists():
+            return cxx, str(Path(runtime).resolve())
+    raise BuildError(f"no C++ compiler with an AddressSanitizer runtime (tried {', '.join(tried) or 'none'})")
+
+
+def sanitizer_environment() -> dict[str, str]:
+    """Environment for a Python process that is to load the checked host build: the
+    sanitizer's runtime preloaded, leak checking off (the interpreter itself never frees
+    everything), and the switch that makes `host_module.host()` pick that build."""
+    cxx, runtime = _sanitizing_compiler()
+    # The C++ runtime goes in with it: the sanitizer hooks exception throwing when it starts, and
+    # the interpreter itself does not link libstdc++.
+    stdcxx = subprocess.run([cxx, "-print-file-name=libstdc++.so.6"], capture_output=True, text=True).stdout.strip()
+    preload = runtime + (" " + str(Path(stdcxx).resolve()) if stdcxx and Path(stdcxx).is_absolute() and Path(stdcxx).exists() else "")
+    return {
+        "LD_PRELOAD": preload,
+        "ASAN_OPTIONS": "detect_leaks=0:abort_on_error=0:halt_on_error=1",
+        "UBSAN_OPTIONS": "print_stacktrace=1:halt_on_error=1",
+        "LLM_INFERENCE_B200_SANITIZE": "1",
+    }
+
+
+def build_host(force: bool = False, sanitize: bool = False) -> Path:
+    """Build (if stale) and return the path of the C++ host extension module; with
+    ``sanitize`` the checked build (in a folder of its own)."""
     import pybind11
 
     sources = sorted(HOST_DIR.glob("*.cpp"))
     headers = sorted(HOST_DIR.glob("*.h"))
-    out = host_module_path()
+    out = host_module_path(sanitize)
+    out.parent.mkdir(parents=True, exist_ok=True)
     includes = ["-I", str(HOST_DIR), "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
-    digest = _digest(sources + headers, CXX_FLAGS + [sys.version])
+    flags = [f for f in CXX_FLAGS if f != "-O2"] + SANITIZE_FLAGS if sanitize else CXX_FLAGS
+    digest = _digest(sources + headers, flags + [sys.version])
     stamp = out.parent / (out.name + ".stamp")
     if not force and out.is_file() and stamp.is_file() and stamp.read_text() == digest:
         return out
     with _locked(out.parent / "host.lock"):
         if not force and out.is_file() and stamp.is_file() and stamp.read_text() == digest:
             return out
-        cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
+        cxx = _sanitizing_compiler()[0] if sanitize else os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++")
         if not cxx:
             raise BuildError("no C++ compiler found (g++ / c++)")
         _compile_all(
-            "C++ host runtime",
+            "C++ host runtime (checked build)" if sanitize else "C++ host runtime",
             sources,
             out,
-            lambda src, obj: [cxx, *CXX_FLAGS, *includes, "-c", str(src), "-o", str(obj)],
-            lambda objs, target: [cxx, "-shared", "-o", str(target), *[str(o) for o in objs]],
+            lambda src, obj: [cxx, *flags, *includes, "-c", str(src), "-o", str(obj)],
+            lambda objs, target: [cxx, "-shared", *(SANITIZE_FLAGS[:1] if sanitize else []), "-o", str(target), *[str(o) for o in objs]],
             digest,
         )
     return out

@@ -216,7 +216,14 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   const int rows_total = q_len * p.group;
   // Later rows attend to more keys: they go first, so the longest blocks do not form the tail.
   const int row_base = static_cast<int>(gridDim.x - 1 - blockIdx.x) * kRows;
-  if (row_base >= rows_total) return;
+  // A block with nothing to do still waits for the kernel in front before it ends: the kernel
+  // behind may pass its own wait once every block of this grid has ended, and must not do so
+  // while this kernel's predecessor still runs.
+  if (row_base >= rows_total) {
+    wait_for_predecessor();
+    let_successor_start();
+    return;
+  }
   const int* table = p.block_table + static_cast<int64_t>(seq) * p.max_pages;
 
   const int first_token = row_base / p.group;
@@ -229,6 +236,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap k_map, const __
   if (num_tiles * pieces_per_tile > kMaxChunks) {
     // The launcher sized the walk from the host's lengths; lengths on the device that exceed
     // them are an error of the caller, reported rather than walked.
+    wait_for_predecessor();
+    let_successor_start();
     if (threadIdx.x == 0) atomicOr(p.err, ERRBIT_BAD_POSITION);
     return;
   }

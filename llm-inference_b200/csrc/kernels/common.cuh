@@ -80,10 +80,13 @@ __device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank
 }
 
 bool b200_overlap_enabled();
+int b200_sm_count_host();  // SMs of the current device (cached)
 
+// `ordered` launches the ordinary way whatever the library's overlap setting: the kernel starts
+// only after everything before it on the stream has finished.
 template <typename... KernelArgs, typename... Args>
-cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
-                          cudaStream_t stream, Args... args) {
+cudaError_t launch_kernel_as(bool ordered, void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -93,8 +96,14 @@ cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, 
   attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = b200_overlap_enabled() ? 1 : 0;
+  config.numAttrs = !ordered && b200_overlap_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+  return launch_kernel_as(false, kernel, grid, block, smem, stream, args...);
 }
 
 template <typename T>

@@ -224,10 +224,12 @@ struct SkinnyPlan {
   int blocks;
 };
 
+constexpr int kSkinnyMaxDevices = 64;
+
 SkinnyPlan plan_skinny(int N, int K) {
   const int tiles = (N + 15) / 16;
   const int chunks = (K + kChunk - 1) / kChunk;
-  const int wave = 2 * 148 * kSkinnyWarps;
+  const int wave = 2 * b200_sm_count_host() * kSkinnyWarps;
   int slices = (wave + tiles / 2) / tiles;            // K slices per 16 rows, over all blocks
   slices = max(1, min(slices, max(1, chunks / 6)));  // every warp keeps a few slabs to stream
   int k_splits = 1;
@@ -243,22 +245,27 @@ SkinnyPlan plan_skinny(int N, int K) {
 template <int MT>
 int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
                   const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
-                  const void* next_weights = nullptr, long long next_bytes = 0) {
+                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
   const size_t ring = static_cast<size_t>(kSkinnyWarps) * SkinnyStages<MT>::value * (2 + MT) * 32 * 16;
   const size_t sums = static_cast<size_t>(k_splits) * block_rows * MT * 8 * sizeof(float);
   const size_t smem = ring > sums ? ring : sums;
-  static bool configured = false;
-  if (!configured) {
+  // The shared-memory opt-in is a property of the function on one device: set once per device.
+  static size_t configured[kSkinnyMaxDevices] = {};
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kSkinnyMaxDevices)
+    return b200_fail("skinny_gemm: cannot tell the current device");
+  if (configured[device] < smem) {
     if (cudaFuncSetAttribute(skinny_gemm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return b200_fail("skinny_gemm: cannot size shared memory");
-    configured = true;
+    configured[device] = smem;
   }
   const dim3 grid(plan.blocks, plan.column_blocks);
-  cudaError_t status = launch_kernel(skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X, Y, M,
-                                     N, K, plan.row_groups, epilogue, scratch, counters, next_weights, next_bytes);
+  cudaError_t status = launch_kernel_as(ordered, skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X,
+                                        Y, M, N, K, plan.row_groups, epilogue, scratch, counters, next_weights,
+                                        next_bytes);
   if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
   return 0;
 }
@@ -384,6 +391,9 @@ B200_API int b200_skinny_gemm_static(const void* W, const void* X, void* Y, int 
   const SkinnyPlan plan = plan_skinny(N, K);
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream);
-  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream);
+  // Launched the ordinary way (no programmatic overlap with the kernel before it): a caller's W may
+  // be the output of that kernel, and this kernel requests its first slabs of W before it would wait.
+  if (M <= 8)
+    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, nullptr, 0, true);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, nullptr, 0, true);
 }

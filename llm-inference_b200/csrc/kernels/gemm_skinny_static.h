@@ -21,6 +21,8 @@
 //  * The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current). Make that first call outside any
 //    stream capture.
+//  * The kernel starts only after everything before it on the stream has finished (it is not
+//    launched for programmatic overlap), so W, like X, may be written by the work just before it.
 //  * All calls on a device share the one array. It keeps whatever the last call left; the
 //    arrival counters, the only part that must start at zero, are cleared on the stream
 //    before every launch. Two calls whose kernels can overlap on the GPU (different streams,

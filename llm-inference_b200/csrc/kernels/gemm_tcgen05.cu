@@ -417,14 +417,19 @@ bool allow_wide_clusters() {
   return true;
 }
 
+// What a parameter sweep (cli/microbench.py) forces instead of the planner's own choices; zeros
+// in normal use. Set through b200_stream_gemm_plan_override, never from the environment.
+struct PlanOverride { int stages = 0, target = 0, members = 0; };
+PlanOverride g_plan_override;
+
 void size_ring(StreamPlan& plan, int k_blocks, int tokens_pad) {
   const size_t x_stride = (static_cast<size_t>(tokens_pad) * kBlockK * 2 + 1023) & ~size_t(1023);
   const size_t stage = static_cast<size_t>(kBlockRows) * kBlockK * 2 + x_stride;
   const int total = plan.blocks * plan.members;
-  const size_t budget = total <= 296 ? 100 * 1024 : 66 * 1024;
+  const size_t budget = total <= 2 * b200_sm_count_host() ? 100 * 1024 : 66 * 1024;
   const int per_block = (k_blocks + plan.members - 1) / plan.members;
   int stages = static_cast<int>(budget / stage);
-  if (const char* forced = getenv("B200_STREAM_STAGES")) stages = atoi(forced);
+  if (g_plan_override.stages > 0) stages = g_plan_override.stages;
   stages = stages > kMaxStages ? kMaxStages : stages;
   stages = stages > per_block ? per_block : stages;
   plan.stages = stages < 2 ? 2 : stages;
@@ -475,13 +480,14 @@ StreamPlan plan_stream_uncached(int N, int K, int tokens_pad) {
   StreamPlan plan;
   plan.blocks = (N + kBlockRows - 1) / kBlockRows;
   const int k_blocks = (K + kBlockK - 1) / kBlockK;
-  int target = 296;  // blocks aimed at: two per SM, so that neighbouring kernels' blocks can share SMs
-  if (const char* forced = getenv("B200_STREAM_TARGET")) target = atoi(forced);
+  const int sms = b200_sm_count_host();
+  int target = 2 * sms;  // blocks aimed at: two per SM, so that neighbouring kernels' blocks can share SMs
+  if (g_plan_override.target > 0) target = g_plan_override.target;
   // Clusters of up to 8 blocks are portable; 16 (which sm_100 schedules when asked) are used
   // when 8 would leave SMs without a block: the 1.5B down product (12 row blocks) went from
   // 10.6 to 8.6 us with them.
-  int widest = plan.blocks * 8 < 148 ? 16 : 8;
-  if (const char* forced = getenv("B200_STREAM_MEMBERS")) widest = atoi(forced);
+  int widest = plan.blocks * 8 < sms ? 16 : 8;
+  if (g_plan_override.members > 0) widest = g_plan_override.members;
   int members = max(1, min(min(widest, kMaxMembers), target / plan.blocks));
   while (members > 1 && k_blocks / members < 3) --members;  // every block keeps a few stages to stream
   plan.members = members;
@@ -490,13 +496,10 @@ StreamPlan plan_stream_uncached(int N, int K, int tokens_pad) {
   // are done, and the product takes half as long again (40 row blocks in clusters of 7 took
   // 16.5 us where clusters of 6 took 11.6 us; 36 in clusters of 8 12.0 us, of 6 8.7 us).
   // Narrow the clusters until they do.
-  if (members > 1 && !getenv("B200_STREAM_MEMBERS")) {
+  if (members > 1 && g_plan_override.members <= 0) {
     StreamPlan narrower = plan;
     while (narrower.members > 1) {
       const int room = clusters_in_flight(narrower.members, narrower.smem);
-      if (getenv("B200_STREAM_DEBUG"))
-        fprintf(stderr, "stream plan N=%d K=%d: %d blocks, clusters of %d (%zu B): room for %d\n", N, K, narrower.blocks,
-                narrower.members, narrower.smem, room);
       if (room == 0 || narrower.blocks <= room) break;
       --narrower.members;
       size_ring(narrower, k_blocks, tokens_pad);
@@ -517,6 +520,8 @@ StreamPlan plan_stream(int N, int K, int tokens_pad) {
   static std::mutex guard;
   static std::vector<Entry> known;
   std::lock_guard<std::mutex> lock(guard);
+  if (g_plan_override.stages > 0 || g_plan_override.target > 0 || g_plan_override.members > 0)
+    return plan_stream_uncached(N, K, tokens_pad);  // a sweep in progress: nothing is remembered
   for (const Entry& e : known)
     if (e.n == N && e.k == K && e.tokens == tokens_pad) return e.plan;
   const StreamPlan plan = plan_stream_uncached(N, K, tokens_pad);
@@ -536,21 +541,20 @@ B200_API int b200_stream_gemm_supported(int M, int N, int K, int epilogue) {
   return 1;
 }
 
-// Kept for symmetry with the other product: this kernel needs no global scratch.
-B200_API void b200_stream_gemm_scratch(int M, int N, int K, int64_t* floats, int* counters) {
-  (void)M; (void)N; (void)K;
-  *floats = 0;
-  *counters = 0;
+// For parameter sweeps only: force the ring depth, the number of blocks aimed at or the cluster
+// width of every later plan (0 = the planner's own choice). Plans made meanwhile are not remembered.
+B200_API void b200_stream_gemm_plan_override(int stages, int target, int members) {
+  g_plan_override.stages = stages;
+  g_plan_override.target = target;
+  g_plan_override.members = members;
 }
 
-B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
-                              float* scratch, int64_t scratch_floats, int* counters, int num_counters, int* err,
+B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
                               const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
   B200_REQUIRE(b200_stream_gemm_supported(M, N, K, epilogue), "stream_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
                "stream_gemm: operands must be 16-byte aligned");
-  (void)scratch; (void)scratch_floats; (void)counters; (void)num_counters;
   StreamParams p;
   p.y = Y;
   p.err = err;

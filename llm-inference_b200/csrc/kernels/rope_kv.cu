@@ -6,7 +6,32 @@
 // store the rotated query densely and the rotated key and the value into the token's page
 // of the layer's arena: row = table[pos / page] * page + pos % page
 // (python/instinct/paged_kv.py:259-265).
+//
+// Pages are handed from request to request without being cleared, and the tensor-core attention
+// kernels load whole tiles of a page and mask the rows past a request's last key only in the
+// scores: what such a row holds still meets a probability of zero in the PV product, and zero
+// times a non-finite leftover would be NaN. So the token that starts a page (position a multiple
+// of the page size: the first write of its request to that page) also clears the rows of the
+// page that this step does not fill. From then on every row of a page a request holds is either
+// the request's own or zero.
 #include "common.cuh"
+
+// Clears rows `first_row .. page_size` of one (page, kv head) tile, which are contiguous.
+template <typename T>
+__device__ __forceinline__ void clear_page_tail(T* tile, int first_row, int page_size, int head_dim) {
+  if (first_row >= page_size) return;
+  const int64_t begin = static_cast<int64_t>(first_row) * head_dim * sizeof(T);
+  const int64_t end = static_cast<int64_t>(page_size) * head_dim * sizeof(T);
+  unsigned char* base = reinterpret_cast<unsigned char*>(tile);
+  if ((static_cast<int64_t>(head_dim) * sizeof(T)) % 16 == 0 && reinterpret_cast<uintptr_t>(base) % 16 == 0) {
+    for (int64_t at = begin + threadIdx.x * 16; at < end; at += static_cast<int64_t>(blockDim.x) * 16)
+      *reinterpret_cast<uint4*>(base + at) = make_uint4(0u, 0u, 0u, 0u);
+  } else {
+    T* elems = tile + static_cast<int64_t>(first_row) * head_dim;
+    const int count = (page_size - first_row) * head_dim;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) elems[i] = from_f32<T>(0.f);
+  }
+}
 
 constexpr int kWideTokens = 64;  // from this many tokens on, one block per token (below)
 
@@ -18,6 +43,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      const float* __restrict__ inv_freq,
                                      const int* __restrict__ positions,
                                      const int* __restrict__ token_seq,
+                                     const int* __restrict__ seq_kv_len,
                                      const int* __restrict__ block_table, int max_pages,
                                      int num_pages, T* __restrict__ k_arena,
                                      T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
@@ -39,6 +65,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
   const int pos = positions[t];
   const int half_rot = rot / 2, half = head_dim / 2;
   T* dst = nullptr;
+  int clear_from = 0;  // for the token that starts a page: the first row this step leaves unwritten
   if (is_q) {
     dst = q_out + (static_cast<int64_t>(t) * q_heads + head) * head_dim;
   } else {
@@ -52,6 +79,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
       } else {
         const int kv_head = is_k ? head - q_heads : head - rotated_heads;
         dst = (is_k ? k_arena : v_arena) + kv_row_offset(page, kv_head, pos % page_size, kv_heads, page_size, head_dim);
+        if (pos % page_size == 0 && seq_kv_len != nullptr) clear_from = max(1, seq_kv_len[token_seq[t]] - pos);
       }
     }
   }
@@ -74,6 +102,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
   wait_for_predecessor();
   let_successor_start();
   if (dst == nullptr) return;
+  if (clear_from > 0) clear_page_tail(dst, clear_from, page_size, head_dim);  // dst is row 0 of the tile
 
   // Pair slot i: below rot/2 it is the rotated pair (i, i + rot/2); the rest are the two
   // trailing dims a partial rotation leaves alone. Value heads are copied (bias added).
@@ -136,6 +165,7 @@ __global__ void rope_kv_write_wide_kernel(const T* __restrict__ qkv, const float
                                           const float* __restrict__ inv_freq,
                                           const int* __restrict__ positions,
                                           const int* __restrict__ token_seq,
+                                          const int* __restrict__ seq_kv_len,
                                           const int* __restrict__ block_table, int max_pages,
                                           int num_pages, T* __restrict__ k_arena,
                                           T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
@@ -164,6 +194,16 @@ __global__ void rope_kv_write_wide_kernel(const T* __restrict__ qkv, const float
         if (threadIdx.x == 0) atomicOr(err, ERRBIT_BAD_PAGE);
       } else {
         kv_row = kv_row_offset(page, 0, pos % page_size, kv_heads, page_size, head_dim);
+        if (pos % page_size == 0 && seq_kv_len != nullptr) {
+          // This token starts the page: clear the rows of every kv head's tile that the step's
+          // later tokens will not fill (kv_row is row 0 of head 0's tile here).
+          const int clear_from = max(1, seq_kv_len[token_seq[t]] - pos);
+          for (int h = 0; h < kv_heads; ++h) {
+            const int64_t tile = kv_row + static_cast<int64_t>(h) * page_size * head_dim;
+            clear_page_tail(k_arena + tile, clear_from, page_size, head_dim);
+            clear_page_tail(v_arena + tile, clear_from, page_size, head_dim);
+          }
+        }
       }
     }
   }
@@ -205,8 +245,10 @@ __global__ void rope_kv_write_wide_kernel(const T* __restrict__ qkv, const float
   }
 }
 
+// `seq_kv_len` (may be null: nothing is cleared then) holds, per request of the step, the number
+// of keys the request has after the step.
 B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float* inv_freq,
-                                const int* positions, const int* token_seq,
+                                const int* positions, const int* token_seq, const int* seq_kv_len,
                                 const int* block_table, int max_pages, int num_pages,
                                 void* k_arena, void* v_arena, void* q_out, int tokens,
                                 int q_heads, int kv_heads, int head_dim, int rot, int page_size,
@@ -223,12 +265,12 @@ B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float*
     const dim3 wide_grid(tokens), wide_block(256);
     if (dtype == DTYPE_F32) {
       launch_kernel(rope_kv_write_wide_kernel<float>, wide_grid, wide_block, angles, stream,
-          static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+          static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, seq_kv_len, block_table,
           max_pages, num_pages, static_cast<float*>(k_arena), static_cast<float*>(v_arena),
           static_cast<float*>(q_out), q_heads, kv_heads, head_dim, page_size, write_kv, err);
     } else if (dtype == DTYPE_BF16) {
       launch_kernel(rope_kv_write_wide_kernel<__nv_bfloat16>, wide_grid, wide_block, angles, stream,
-          static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+          static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, seq_kv_len, block_table,
           max_pages, num_pages, static_cast<__nv_bfloat16*>(k_arena),
           static_cast<__nv_bfloat16*>(v_arena), static_cast<__nv_bfloat16*>(q_out), q_heads,
           kv_heads, head_dim, page_size, write_kv, err);
@@ -243,12 +285,12 @@ B200_API int b200_rope_kv_write(const void* qkv, const float* bias, const float*
   B200_REQUIRE(grid.y <= 65535, "rope_kv_write: too many heads");
   if (dtype == DTYPE_F32) {
     launch_kernel(rope_kv_write_kernel<float>, grid, dim3(threads), smem, stream,
-        static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+        static_cast<const float*>(qkv), bias, inv_freq, positions, token_seq, seq_kv_len, block_table,
         max_pages, num_pages, static_cast<float*>(k_arena), static_cast<float*>(v_arena),
         static_cast<float*>(q_out), q_heads, kv_heads, head_dim, rot, page_size, write_kv, err);
   } else if (dtype == DTYPE_BF16) {
     launch_kernel(rope_kv_write_kernel<__nv_bfloat16>, grid, dim3(threads), smem, stream,
-        static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, block_table,
+        static_cast<const __nv_bfloat16*>(qkv), bias, inv_freq, positions, token_seq, seq_kv_len, block_table,
         max_pages, num_pages, static_cast<__nv_bfloat16*>(k_arena),
         static_cast<__nv_bfloat16*>(v_arena), static_cast<__nv_bfloat16*>(q_out), q_heads,
         kv_heads, head_dim, rot, page_size, write_kv, err);

@@ -669,8 +669,8 @@ B200_API int b200_argmax_rows(const float* logits, int rows, int vocab, int64_t 
                               cudaStream_t stream) {
   if (rows == 0) return 0;
   B200_REQUIRE(rows > 0 && vocab > 0 && row_stride >= vocab, "argmax_rows: bad sizes");
-  if (best != nullptr && arrived != nullptr && rows < 148 && vocab >= 4096) {
-    int slices = (2 * 148 + rows - 1) / rows;
+  if (best != nullptr && arrived != nullptr && rows < b200_sm_count_host() && vocab >= 4096) {
+    int slices = (2 * b200_sm_count_host() + rows - 1) / rows;
     slices = slices > 64 ? 64 : slices;
     launch_kernel(argmax_slices_kernel, dim3(slices, rows), dim3(kArgmaxSliceThreads), 0, stream, logits, vocab,
                   row_stride, row_index, out, best, arrived);
@@ -701,7 +701,7 @@ B200_API int b200_sample_rows(const float* logits, int rows, int vocab, int64_t 
     B200_REQUIRE(scratch_bytes >= b200_sample_scratch_bytes(rows), "sample_rows: scratch too small");
     RowScratch* state = static_cast<RowScratch*>(scratch);
     if (vocab > kListCap) {
-      int slices = (2 * 148 + rows - 1) / rows;
+      int slices = (2 * b200_sm_count_host() + rows - 1) / rows;
       slices = slices > 64 ? 64 : slices;
       const dim3 grid(slices, rows);
       for (int shift = 24; shift >= 0; shift -= 8)

@@ -50,7 +50,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_embedding_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "b200_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     "b200_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "b200_rope_kv_write": [c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 8 + [c_void_p, c_void_p],
+    "b200_rope_kv_write": [c_void_p] * 7 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 8 + [c_void_p, c_void_p],
     "b200_paged_attention_plain": [c_void_p] * 6
     + [c_int, c_int, c_void_p]
     + [c_int] * 6
@@ -60,7 +60,7 @@ _SIGNATURES: dict[str, list] = {
     "b200_paged_decode_attention_tma": [c_void_p] * 8 + [c_int] * 8 + [c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "b200_flash_prefill_tcgen05": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_void_p, c_void_p],
     "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p],
-    "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_void_p],
+    "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p],
     "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p, c_int64, c_void_p],
 }
@@ -84,8 +84,9 @@ class KernelLibrary:
         self.lib.b200_skinny_gemm_scratch.restype = None
         self.lib.b200_stream_gemm_supported.argtypes = [c_int] * 4
         self.lib.b200_stream_gemm_supported.restype = c_int
-        self.lib.b200_stream_gemm_scratch.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]
-        self.lib.b200_stream_gemm_scratch.restype = None
+        self.lib.b200_stream_gemm_plan_override.argtypes = [c_int] * 3
+        self.lib.b200_stream_gemm_plan_override.restype = None
+        self.lib.b200_sm_count.restype = c_int
         self._functions = {}
         self.calls = 0  # kernel launches issued through this library
         for name, argtypes in _SIGNATURES.items():

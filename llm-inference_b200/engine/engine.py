@@ -100,6 +100,7 @@ class Engine:
         cuda_graphs: bool = True,
         run_ahead: bool = True,
         kernels: str = "tuned",
+        nvtx: bool = False,
         model: Model | None = None,
     ) -> None:
         if kernels not in ("tuned", "plain"):
@@ -148,14 +149,21 @@ class Engine:
             # "plain": the plain attention kernel and the library's matrix products everywhere (the
             # slow, simple kernels the tuned ones are checked against); "tuned": each step's best.
             options={
-                "cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens,
+                "cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens, "nvtx": bool(nvtx),
                 **({"attention": "plain", "gemm": "library"} if kernels == "plain" else {}),
             },
         )
+        # `nvtx=True` names ranges for a profiler's timeline: "step ..." around each model step,
+        # "layer N" and "head" inside it, "sample" around the sampling kernels (the reference's
+        # include/instinct/nvtx.h:9-24 and its uses). Off by default; host-side marks only.
+        self.nvtx = bool(nvtx)
         self.sampler = Sampler(self.device, max_num_sequences)
         # While a decode step's tokens travel to the host, the next step may already run (see
-        # ModelRunner.step_ahead); `run_ahead=False` keeps every step behind the host.
-        self.run_ahead = bool(run_ahead) and self.runner.use_graphs
+        # ModelRunner.step_ahead); `run_ahead=False` keeps every step behind the host. A step
+        # launched ahead may be dropped, which is harmless for paged keys and values (the same
+        # numbers get written again) and not for per-request state that a step advances: a model
+        # with such state never runs ahead.
+        self.run_ahead = bool(run_ahead) and self.runner.use_graphs and not self.cache.state_specs
         self._ahead = None
         self.steps_ahead_used = 0
         self.steps_ahead_dropped = 0
@@ -246,12 +254,18 @@ class Engine:
             wanting = [e for e in entries if e.wants_token]
             if wanting:
                 requests = [self.scheduler.request(e.request_id) for e in wanting]
-                rows = self.sampler.launch(
-                    logits,
-                    [r.sampling for r in requests],
-                    [self.scheduler.draw_key(r.request_id) for r in requests],
-                    self.runner.err,
-                )
+                if self.nvtx:
+                    torch.cuda.nvtx.range_push("sample")
+                try:
+                    rows = self.sampler.launch(
+                        logits,
+                        [r.sampling for r in requests],
+                        [self.scheduler.draw_key(r.request_id) for r in requests],
+                        self.runner.err,
+                    )
+                finally:
+                    if self.nvtx:
+                        torch.cuda.nvtx.range_pop()
                 if self.run_ahead and self.scheduler.repeats(plan):
                     # The next step will feed these tokens to the same requests unless one of
                     # them ends a request: launch it now, behind the sampling kernels.

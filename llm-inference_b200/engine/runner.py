@@ -181,12 +181,19 @@ class ModelRunner:
 
         ordered = [entries[i] for i in order]
         ordered_starts = [starts[i] for i in order]
-        if self.use_graphs and total == len(entries) and len(entries) <= self.cache.max_num_sequences:
-            logits = self._decode_graph(ordered, ordered_starts, wanted_rows)
-        else:
-            ctx = self._build_context(ordered, ordered_starts, wanted_rows)
-            tables = self._tables
-            logits = self.model.forward(ctx, lambda call: self._view(call, tables))
+        nvtx = bool(self.options.get("nvtx"))
+        if nvtx:  # one range per step, named for what it holds (cuda/engine.cu:53,75 in the reference)
+            torch.cuda.nvtx.range_push(f"step {self.steps}: {len(entries)} requests, {total} tokens")
+        try:
+            if self.use_graphs and total == len(entries) and len(entries) <= self.cache.max_num_sequences:
+                logits = self._decode_graph(ordered, ordered_starts, wanted_rows)
+            else:
+                ctx = self._build_context(ordered, ordered_starts, wanted_rows)
+                tables = self._tables
+                logits = self.model.forward(ctx, lambda call: self._view(call, tables))
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
         for e, start in zip(entries, starts):
             manager.advance(e.request_id, start + len(e.tokens))
         self.steps += 1
@@ -365,7 +372,7 @@ class ModelRunner:
             q_start[real:] = np.arange(real, s, dtype=np.int32)
             q_len[real:] = 1
             kv_len[real:] = 1
-            slot[real:] = -1
+            slot[real:] = self.cache.null_slot()
             for group in self.cache.groups:
                 table_views[group.index][real:] = self.cache.null_page(group)
             decode = s

@@ -43,6 +43,7 @@ class GroupedQueryAttention(Part):
         self.qkv_bias, self.window = qkv_bias, int(window)
         self.scale = float(scale) if scale is not None else head_dim**-0.5
         self.position = build_part("position", position)
+        self.graph_safe = self.position.graph_safe
         self.w_qkv = self.b_qkv = self.w_o = None
 
     def cache_spec(self) -> KVCacheSpec:
@@ -78,9 +79,9 @@ class GroupedQueryAttention(Part):
         width = (self.q_heads + 2 * self.kv_heads) * self.head_dim
         qkv = ops.linear(ctx, h, self.w_qkv, ctx.buffer("qkv", (t, width)))
         q = ctx.buffer("q", (t, self.q_heads * self.head_dim))
-        ops.rope_kv_write(
-            ctx, cache, qkv, self.b_qkv, self.position.inv_freq, q, self.q_heads, self.kv_heads, self.head_dim
-        )
+        # Bias, position encoding and the cache write are the position part's: the mixer does not
+        # know how positions are encoded.
+        self.position.apply(ctx, cache, qkv, self.b_qkv, q, self.q_heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn", (t, self.q_heads * self.head_dim))
         self.attend(ctx, cache, q, attn)
         return ops.linear(ctx, attn, self.w_o, ctx.buffer("branch", (t, self.hidden_size)))

@@ -45,7 +45,7 @@ def attend(
     if decode_seqs:
         reach = ctx.max_kv_len if not cache.window else min(ctx.max_kv_len, cache.window + 64)
         tma = ops.decode_uses_tma(ctx, decode_seqs, q_heads, kv_heads, head_dim, cache.page_size)
-        splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(decode_seqs, kv_heads, reach, tma)
+        splits = int(ctx.options.get("decode_splits", 0)) or ops.decode_splits(decode_seqs, kv_heads, reach, tma, ops.sm_count(ctx))
         ops.paged_flash_attention(
             ctx, cache, q, out, q_heads, kv_heads, head_dim, scale,
             first_seq=0, num_seqs=decode_seqs, decode=True, max_q_len=1, splits=splits,

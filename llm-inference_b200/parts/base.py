@@ -11,8 +11,11 @@ Kinds of part and what each must provide:
                   output ``delta`` into the 32-bit residual stream ``x`` and returns the
                   normalised rows in the compute dtype (only ``rows`` if given, without
                   touching ``x``).
-``position``      owned by a mixer: turns positions into whatever the mixer's kernel needs
-                  (a table of inverse frequencies for rotary encodings).
+``position``      owned by an attention mixer:
+                  ``apply(ctx, cache, qkv, bias, q_out, q_heads, kv_heads, head_dim)`` adds the
+                  projection bias, encodes each token's position into its queries and keys,
+                  writes keys and values to the token's page and the queries to ``q_out``; the
+                  mixer never looks inside (the rotary part does it in one fused kernel).
 ``mixer``         ``cache_spec() -> KVCacheSpec | StateSpec | None`` and
                   ``forward(ctx, cache, h) -> Tensor`` where ``cache`` is the
                   :class:`CacheView` of the layer call.

@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+from contextlib import contextmanager
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -10,6 +11,20 @@ import torch
 from ..weights.loader import TensorSpec
 from .base import KVCacheSpec, PartSpec, StateSpec, build_part
 from .context import CacheView, StepContext
+
+
+@contextmanager
+def _nvtx_range(name: str):
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
+@contextmanager
+def _no_range(name: str):
+    yield
 
 
 @dataclass(frozen=True)
@@ -121,13 +136,19 @@ class Model:
         """Run the step's tokens through every layer call; return 32-bit logits of
         ``ctx.logit_rows`` as ``[wanted, vocab]``. ``cache_views(call)`` yields the call's
         :class:`CacheView`."""
+        # With options["nvtx"] every layer call and the head get a named range, as the reference
+        # marks them (cuda/qwen_model.cu:106,138,169); the ranges are host-side marks around the
+        # launches and change nothing on the device.
+        mark = _nvtx_range if ctx.options.get("nvtx") else _no_range
         x = self.embedding.forward(ctx)
         delta = None
         for call in self.schedule:
             block = self.blocks[call.layer]
             view: CacheView | None = cache_views(call) if block.cache_spec() is not None else None
-            delta = block.forward(ctx, view, x, delta)
+            with mark(f"layer {call.layer}"):
+                delta = block.forward(ctx, view, x, delta)
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.head.vocab_size), dtype=torch.float32, device=ctx.device)
-        h = self.final_norm.forward(ctx, x, delta, rows=ctx.logit_rows, out_name="normed_rows")
-        return self.head.forward(ctx, h)
+        with mark("head"):
+            h = self.final_norm.forward(ctx, x, delta, rows=ctx.logit_rows, out_name="normed_rows")
+            return self.head.forward(ctx, h)

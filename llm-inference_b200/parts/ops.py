@@ -147,33 +147,17 @@ def linear_swiglu(ctx: StepContext, x: torch.Tensor, weight: torch.Tensor, out: 
     return True
 
 
-_GEMM_SCRATCH: dict[tuple[str, int, int, int], tuple[int, int]] = {}  # (kernel, m, n, k) -> (floats, counters)
+_SKINNY_SCRATCH: dict[tuple[int, int, int], tuple[int, int]] = {}  # (m, n, k) -> (floats, counters)
 
 
 def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int) -> None:
-    """Launch a weight-streaming product; its scratch (partial sums of blocks that share
-    rows of the weight matrix, and their arrival counters) lives in the step's workspace."""
-    from ctypes import byref
+    """Launch a weight-streaming product. The mma.sync kernel keeps the partial sums of blocks
+    that share rows of the weight matrix, and their arrival counters, in the step's workspace;
+    the tcgen05 kernel reduces inside its clusters and needs none."""
+    from ctypes import byref, c_void_p
 
     m, k = x.shape
     n = weight.shape[0]
-    key = (kernel, m, n, k)
-    need = _GEMM_SCRATCH.get(key)
-    if need is None:
-        floats, counters = c_int64(0), c_int(0)
-        getattr(ctx.lib.lib, f"b200_{kernel}_gemm_scratch")(m, n, k, byref(floats), byref(counters))
-        need = _GEMM_SCRATCH[key] = (floats.value, counters.value)
-    floats, counters = need
-    scratch = counter_buf = None
-    if floats:
-        scratch = ctx.buffer("gemm_partials", (floats,), torch.float32, per_token=False)
-        counter_buf = ctx.workspace.zeros("gemm_counters", max(counters, 4096), torch.int32)
-    args = [
-        ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue), ptr(scratch), c_int64(floats),
-        ptr(counter_buf), c_int(counter_buf.numel() if counter_buf is not None else 0),
-    ]
-    if kernel == "stream":
-        args.append(ptr(ctx.err))
     # The weights of the product that follows this one in the step, if the runner has learnt the
     # order: this kernel asks the L2 cache to fetch them while it runs.
     trace = ctx.options.get("gemm_trace")
@@ -181,12 +165,27 @@ def _small_gemm(ctx: StepContext, kernel: str, x: torch.Tensor, weight: torch.Te
         trace.append((weight.data_ptr(), weight.numel() * weight.element_size()))
     upcoming = ctx.options.get("gemm_next", {}).get(weight.data_ptr())
     if upcoming is not None:
-        from ctypes import c_void_p
-
-        args += [c_void_p(upcoming[0]), c_int64(min(upcoming[1], ctx.options.get("prefetch_bytes", 64 << 20)))]
+        prefetch = [c_void_p(upcoming[0]), c_int64(min(upcoming[1], ctx.options.get("prefetch_bytes", 64 << 20)))]
     else:
-        args += [ptr(None), c_int64(0)]
-    ctx.lib.call(f"b200_{kernel}_gemm", *args, ctx.stream)
+        prefetch = [ptr(None), c_int64(0)]
+    head = [ptr(weight), ptr(x), ptr(out), c_int(m), c_int(n), c_int(k), c_int(epilogue)]
+    if kernel == "stream":
+        ctx.lib.call("b200_stream_gemm", *head, ptr(ctx.err), *prefetch, ctx.stream)
+        return
+    need = _SKINNY_SCRATCH.get((m, n, k))
+    if need is None:
+        floats, counters = c_int64(0), c_int(0)
+        ctx.lib.lib.b200_skinny_gemm_scratch(m, n, k, byref(floats), byref(counters))
+        need = _SKINNY_SCRATCH[(m, n, k)] = (floats.value, counters.value)
+    floats, counters = need
+    scratch = counter_buf = None
+    if floats:
+        scratch = ctx.buffer("gemm_partials", (floats,), torch.float32, per_token=False)
+        counter_buf = ctx.workspace.zeros("gemm_counters", max(counters, 4096), torch.int32)
+    ctx.lib.call(
+        "b200_skinny_gemm", *head, ptr(scratch), c_int64(floats), ptr(counter_buf),
+        c_int(counter_buf.numel() if counter_buf is not None else 0), *prefetch, ctx.stream,
+    )
 
 
 def embedding_gather(ctx: StepContext, table: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -253,8 +252,8 @@ def rope_kv_write(
     _need(cache.keys.dtype == qkv.dtype and cache.values.dtype == qkv.dtype, "rope_kv_write: cache dtype differs")
     ctx.lib.call(
         "b200_rope_kv_write", ptr(qkv), ptr(bias), ptr(inv_freq), ptr(ctx.positions), ptr(ctx.token_seq),
-        ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages), ptr(cache.keys), ptr(cache.values),
-        ptr(q_out), c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(rot),
+        ptr(getattr(ctx, "seq_kv_len", None)), ptr(cache.block_table), c_int(cache.max_pages), c_int(cache.num_pages),
+        ptr(cache.keys), ptr(cache.values), ptr(q_out), c_int(tokens), c_int(q_heads), c_int(kv_heads), c_int(head_dim), c_int(rot),
         c_int(cache.page_size), c_int(1 if cache.writes else 0), c_int(dtype_code(qkv.dtype)), ptr(ctx.err), ctx.stream,
     )
     return q_out
@@ -293,7 +292,7 @@ def paged_attention_plain(
     return out
 
 
-NUM_SMS = 148
+NUM_SMS = 148  # a B200; only what `decode_splits` assumes when no device is asked (tests on the CPU)
 DECODE_STAGES = 3  # pieces in flight per warp of the TMA decode kernel
 MAX_DECODE_SPLITS = 64  # what the merge kernel takes in one round trip
 
@@ -313,7 +312,12 @@ def decode_uses_tma(ctx: StepContext, num_seqs: int, q_heads: int, kv_heads: int
     return True
 
 
-def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = False) -> int:
+def sm_count(ctx: StepContext) -> int:
+    """SMs of the device the step runs on (the library asks the device once)."""
+    return int(ctx.lib.lib.b200_sm_count())
+
+
+def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = False, num_sms: int = NUM_SMS) -> int:
     """How many blocks cut each request's keys in a decode step: at least one 64-key tile
     each, and few enough that the merge of their partial results stays cheap. The cp.async
     kernel (three blocks per SM) wants about two waves of blocks. The TMA kernel (rings three
@@ -326,7 +330,7 @@ def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = Fal
     2.17 ms): the wider merge costs what the two extra splits gain."""
     tiles = max(1, (max_kv_len + 63) // 64)
     pairs = max(1, num_seqs * kv_heads)
-    want = (2 if tma else 6) * NUM_SMS // pairs  # rounded down: one block too many would start another wave
+    want = (2 if tma else 6) * num_sms // pairs  # rounded down: one block too many would start another wave
     most = 16 if want < 32 else max(16, min(MAX_DECODE_SPLITS, tiles // 4))
     return max(1, min(tiles, most, want))
 

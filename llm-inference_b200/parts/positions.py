@@ -5,7 +5,9 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from . import ops
 from .base import Part, register_part
+from .context import CacheView, StepContext
 
 
 class RotaryEncoding(Part):
@@ -29,6 +31,24 @@ class RotaryEncoding(Part):
 
     def load(self, tensors, dtype, device) -> None:
         self.inv_freq = torch.from_numpy(self.table()).to(device)
+
+    def apply(
+        self,
+        ctx: StepContext,
+        cache: CacheView,
+        qkv: torch.Tensor,
+        bias: torch.Tensor | None,
+        q_out: torch.Tensor,
+        q_heads: int,
+        kv_heads: int,
+        head_dim: int,
+    ) -> torch.Tensor:
+        """The position part's one duty towards an attention mixer: take the step's projected
+        rows ``qkv`` (``[tokens, (q_heads + 2 kv_heads) * head_dim]``, bias not yet added), add
+        the bias, encode each token's position into its queries and keys, store keys and values
+        in the token's page of ``cache`` (unless ``cache.writes`` is false) and the queries
+        densely in ``q_out``. Here all of it is one kernel."""
+        return ops.rope_kv_write(ctx, cache, qkv, bias, self.inv_freq, q_out, q_heads, kv_heads, head_dim)
 
 
 register_part("position", "rotary", RotaryEncoding)

@@ -91,3 +91,18 @@ def test_replay_checks_its_options_and_needs_a_gpu(tmp_path):
     if not torch.cuda.is_available():
         result = subprocess.run(base + ["--max-tokens", "64"], input=step, capture_output=True, text=True, timeout=300)
         assert result.returncode == 2 and "no CUDA device" in result.stderr and "done" not in result.stdout
+
+
+def test_benchmark_percentiles_interpolate_as_the_reference_does():
+    """The reference's rule (python/instinct/benchmark.py:94-107): rank q (n - 1), linear between
+    the neighbours. Checked on values whose percentiles are easy to state."""
+    import math
+
+    from llm_inference_b200.cli.benchmark import percentiles
+
+    values = [float(v) for v in range(101)]  # rank q * 100 is the value itself
+    assert percentiles(values[::-1]) == {"p50": 50.0, "p95": 95.0, "p99": 99.0}
+    got = percentiles([1.0, 2.0, 3.0, 4.0, 10.0])
+    assert got["p50"] == 3.0 and math.isclose(got["p95"], 4.0 + 0.8 * 6.0) and math.isclose(got["p99"], 4.0 + 0.96 * 6.0)
+    assert percentiles([7.0]) == {"p50": 7.0, "p95": 7.0, "p99": 7.0}
+    assert all(math.isnan(v) for v in percentiles([]).values())

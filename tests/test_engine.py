@@ -298,3 +298,51 @@ def test_random_workloads_are_the_same_with_and_without_running_ahead(tiny, seed
     behind, _ = scenario(False)
     assert ahead == behind
     assert stats["steps_ahead_used"] > 0 and stats["steps_ahead_dropped"] > 0
+
+
+@pytest.mark.parametrize("where", ["model step", "sampler"])
+def test_a_failing_step_cancels_its_requests_and_the_engine_goes_on(tiny, where):
+    """What the reference does when a step throws (python/instinct/mlx_engine.py:419-423,
+    cuda/engine.cu:85-89,108-112): every request of that step ends as cancelled with reason
+    "error", what they held goes back, the error reaches the caller, and the engine serves
+    the next request. The failure is made on the host: the model step (or the sampler's
+    launch) is replaced by a function that raises."""
+    name, folder, config, weights = tiny
+    rng = np.random.default_rng(31)
+    prompts = [random_tokens(rng, config["vocab_size"], n) for n in (6, 11, 4)]
+
+    class Injected(RuntimeError):
+        pass
+
+    with engine_for(name, folder) as engine:
+        a, b = engine.submit(prompts[0], 30), engine.submit(prompts[1], 30)
+        for _ in range(6):  # both are decoding by now, and a step launched ahead is in flight
+            engine.step()
+        assert engine.request(a).state.value == "running" and engine.request(b).state.value == "running"
+        assert engine._ahead is not None
+        waiting = engine.submit(prompts[2], 5)  # admitted by the failing step's plan: part of it
+        target, attribute = (engine.runner, "step") if where == "model step" else (engine.sampler, "launch")
+        original = getattr(target, attribute)
+
+        def fail(*args, **kwargs):
+            raise Injected("injected on the host")
+
+        setattr(target, attribute, fail)
+        with pytest.raises(Injected):
+            engine.step()
+        setattr(target, attribute, original)
+        for rid in (a, b, waiting):
+            view = engine.request(rid)
+            assert view.state.value == "cancelled" and view.reason == "error", (rid, view.state, view.reason)
+        assert engine._ahead is None and not engine.has_work() and drained(engine)
+        engine.cache.manager.check_invariants()
+        # The engine is still good: a new request gets the plain implementation's tokens.
+        assert engine.generate(prompts[1], 8) == plain.greedy(config, weights, prompts[1], 8)
+        # generate() itself: the failing request is cancelled and forgotten, the error re-raised.
+        setattr(target, attribute, fail)
+        before = engine.stats()["cancelled"]
+        with pytest.raises(Injected):
+            engine.generate(prompts[0], 4)
+        setattr(target, attribute, original)
+        assert engine.stats()["cancelled"] == before + 1 and not engine.has_work() and drained(engine)
+        assert engine.generate(prompts[2], 5) == plain.greedy(config, weights, prompts[2], 5)

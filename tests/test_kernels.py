@@ -258,7 +258,7 @@ def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page, runs)
     keys = torch.full((num_pages, kv_heads, page, head_dim), 7.0, device="cuda", dtype=dtype)
     values = keys.clone()
     q_out = torch.empty(t, q_heads * head_dim, device="cuda", dtype=dtype)
-    ctx = make_ctx(lib, positions=positions, token_seq=token_seq)
+    ctx = make_ctx(lib, positions=positions, token_seq=token_seq, starts=starts, runs=runs)
     table_dev = torch.from_numpy(tables).cuda()
     view = CacheView(0, True, keys, values, table_dev, num_pages, tables.shape[1], page)
     ops.rope_kv_write(ctx, view, qkv, bias, inv_freq, q_out, q_heads, kv_heads, head_dim)
@@ -283,10 +283,19 @@ def test_rope_kv_write(lib, dtype, q_heads, kv_heads, head_dim, rot, page, runs)
         touched[pg, r] = True
         np.testing.assert_allclose(keys[pg, :, r].double().cpu().numpy(), k_rot[row], **kw)
         np.testing.assert_allclose(values[pg, :, r].double().cpu().numpy(), v[row], **kw)
-    # Nothing else in the arena was written.
-    untouched = ~touched
-    assert torch.all(keys.float().cpu().permute(0, 2, 1, 3)[untouched] == 7.0)
-    assert torch.all(values.float().cpu().permute(0, 2, 1, 3)[untouched] == 7.0)
+    # The token that starts a page clears the rows of it that the step does not fill (leftovers of
+    # the page's last owner must not reach a PV product); nothing else in the arena was written.
+    cleared = torch.zeros(num_pages, page, dtype=torch.bool)
+    for pos, s in zip(positions, token_seq):
+        if pos % page == 0:
+            for r in range(1, page):
+                if pos + r >= seq_lens[s]:
+                    cleared[int(tables[s, pos // page]), r] = True
+    assert not bool((cleared & touched).any()) and bool(cleared.any())
+    untouched = ~touched & ~cleared
+    for arena in (keys, values):
+        rows = arena.float().cpu().permute(0, 2, 1, 3)
+        assert torch.all(rows[untouched] == 7.0) and torch.all(rows[cleared] == 0.0)
     # A call that only reads another layer's cache rotates the queries and writes nothing.
     before = keys.clone()
     view.writes = False

@@ -248,9 +248,100 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         assert engine.stats()["free_state_slots"] == 3
 
 
+def test_graph_safe_mixer_with_state_is_replayed_but_never_run_ahead(tmp_path):
+    """The running-mean mixer again, written with device-side operations only, so that its
+    decode steps replay a captured graph. A decode step launched ahead and then dropped would
+    advance its state twice: an engine whose model keeps per-request state does not run ahead,
+    and the stop token, cancel, late submit and forced token below cost nothing."""
+    from helpers import plain_weights
+    from llm_inference_b200 import create_engine
+    from llm_inference_b200.parts import Part, StateSpec, register_part
+    from llm_inference_b200.weights import TensorSpec, write_model_folder
+
+    ToyConfig = register_toy()
+
+    class DeviceRunningMean(Part):
+        graph_safe = True
+
+        def __init__(self, *, prefix: str, hidden_size: int) -> None:
+            self.prefix, self.hidden_size = prefix, hidden_size
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "mix.weight", (self.hidden_size, self.hidden_size))]
+
+        def load(self, tensors, dtype, device):
+            self.weight = tensors[self.prefix + "mix.weight"].to(device=device, dtype=dtype)
+
+        def cache_spec(self):
+            return StateSpec(((self.hidden_size,), (1,)), (torch.float32, torch.float32))
+
+        def forward(self, ctx, cache, h):
+            sums, counts = cache.state
+            seq = ctx.token_seq.long()
+            first = ctx.seq_q_start.long()
+            slots = ctx.seq_slot.long()
+            total = torch.cumsum(h.float(), 0)
+            inside = total - (total[first] - h.float()[first])[seq]  # running sum within each request's run
+            index = torch.arange(h.shape[0], device=h.device) - first[seq]
+            running = sums[slots][seq] + inside
+            seen = counts[slots][seq] + (index + 1).float()[:, None]
+            last = first + ctx.seq_q_len.long() - 1
+            sums.index_copy_(0, slots, running[last])
+            counts.index_copy_(0, slots, seen[last])
+            return (running / seen).to(h.dtype) @ self.weight.t()
+
+    register_part("mixer", "running_mean", DeviceRunningMean, replace=True)
+    try:
+        config = ToyConfig("ToyStateForCausalLM", 97, 48, 2, 96, (), 80, 1e-6)
+        folder = write_model_folder(tmp_path / "toy", config, seed=5, std=0.2)
+        raw, weights = plain_weights(folder)
+        rng = np.random.default_rng(1)
+        prompts = [[int(t) for t in rng.integers(0, 97, n)] for n in (7, 12, 3, 9)]
+
+        def greedy(prompt, count):
+            tokens, out = list(prompt), []
+            for _ in range(count):
+                out.append(int(np.argmax(toy_plain(raw, weights, tokens)[-1])))
+                tokens.append(out[-1])
+            return out
+
+        long = greedy(prompts[0], 30)
+        stop = long[13]
+        with create_engine(folder, dtype="float32", max_num_sequences=4, kv_cache_bytes=1 << 20, page_size=8,
+                           prefill_chunk_size=4, prefill_burst_size=6, run_ahead=True) as engine:
+            assert engine.runner.use_graphs and not engine.run_ahead
+            a = engine.submit(prompts[0], 30, [stop])
+            b = engine.submit(prompts[1], 24)
+            c = engine.submit(prompts[2], 40)
+            steps, late = 0, None
+            while engine.has_work():
+                engine.step()
+                steps += 1
+                if steps == 9:
+                    engine.cancel(c)
+                if steps == 14:
+                    late = engine.submit(prompts[3], 10)
+                if steps == 18:
+                    engine.force(b, [1])
+            assert engine.runner.graph_replays > 10
+            assert engine.stats()["steps_ahead_used"] == 0 and engine.stats()["steps_ahead_dropped"] == 0
+            assert engine.request(a).output == long[: long.index(stop) + 1]
+            assert engine.request(late).output == greedy(prompts[3], 10)
+            got_b = engine.request(b).output
+            forced_at = got_b.index(1, 0) if 1 in got_b else None
+            assert forced_at is not None
+            # Up to the forced token b follows its own greedy path, and after it the path from there.
+            assert got_b[:forced_at] == greedy(prompts[1], forced_at)
+            assert got_b[forced_at + 1 :] == greedy(prompts[1] + got_b[: forced_at + 1], len(got_b) - forced_at - 1)
+            assert engine.stats()["free_state_slots"] == 4
+    finally:
+        register_toy()  # the host-side mixer again, for whichever test runs next
+
+
 def register_routed_toy():
-    """A second toy architecture, defined here only: the stock attention mixer with another
-    position encoding (rotary angles of position / 4, as position interpolation does), a routed
+    """A second toy architecture, defined here only: the stock attention mixer with two other
+    position encodings (rotary angles of position / 4, as position interpolation does, and in
+    the last layer learned per-position offsets, which have no frequency table at all), a routed
     feed-forward (two experts, the better one per token by a 32-bit router) in the odd layers and
     the stock SwiGLU in the even ones, and a run order that visits layer 0 twice."""
     from dataclasses import dataclass
@@ -258,19 +349,51 @@ def register_routed_toy():
     from llm_inference_b200.config import ModelConfig, register_architecture
     from llm_inference_b200.parts.base import Part, PartSpec, register_part
     from llm_inference_b200.parts.model import LayerCall, ModelRecipe
+    from llm_inference_b200.parts.positions import RotaryEncoding
     from llm_inference_b200.weights.loader import TensorSpec
 
-    class SquashedRotary(Part):
-        """Rotary encoding at ``position / factor``: all the mixer asks of a position part is
-        the table of inverse frequencies it multiplies positions with."""
+    class SquashedRotary(RotaryEncoding):
+        """Rotary encoding at ``position / factor``: the stock rotary part with another table of
+        inverse frequencies."""
 
         def __init__(self, *, head_dim: int, theta: float, factor: float) -> None:
-            self.head_dim, self.theta, self.factor = head_dim, float(theta), float(factor)
-            self.inv_freq = None
+            super().__init__(head_dim=head_dim, theta=theta)
+            self.factor = float(factor)
+
+        def table(self):
+            return (plain.rope_inverse_frequencies(self.head_dim, self.theta) / np.float32(self.factor)).astype(np.float32)
+
+    class LearnedOffset(Part):
+        """No rotation and no frequency table: a learned vector per position, added to every
+        query and key head. Written with torch operations on the step's device metadata, which
+        is all the mixer's contract with its position part asks for."""
+
+        graph_safe = False
+
+        def __init__(self, *, prefix: str, head_dim: int, max_positions: int) -> None:
+            self.prefix, self.head_dim, self.max_positions = prefix, head_dim, max_positions
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "position_offset.weight", (self.max_positions, self.head_dim))]
 
         def load(self, tensors, dtype, device):
-            table = plain.rope_inverse_frequencies(self.head_dim, self.theta) / np.float32(self.factor)
-            self.inv_freq = torch.from_numpy(table.astype(np.float32)).to(device)
+            self.offsets = tensors[self.prefix + "position_offset.weight"].to(device=device, dtype=torch.float32)
+
+        def apply(self, ctx, cache, qkv, bias, q_out, q_heads, kv_heads, head_dim):
+            t, d = qkv.shape[0], head_dim
+            rows = qkv.float() if bias is None else qkv.float() + bias
+            positions = ctx.positions.long()
+            offset = self.offsets[positions][:, None, :]
+            q = rows[:, : q_heads * d].view(t, q_heads, d) + offset
+            k = rows[:, q_heads * d : (q_heads + kv_heads) * d].view(t, kv_heads, d) + offset
+            v = rows[:, (q_heads + kv_heads) * d :].view(t, kv_heads, d)
+            q_out.copy_(q.reshape(t, q_heads * d))
+            if cache.writes:
+                page = cache.block_table[ctx.token_seq.long(), positions // cache.page_size].long()
+                row = positions % cache.page_size
+                cache.keys[page, :, row] = k.to(cache.keys.dtype)
+                cache.values[page, :, row] = v.to(cache.values.dtype)
+            return q_out
 
     class TwoExperts(Part):
         """``out = p * expert_e(h)`` with ``e = argmax(router(h))`` and ``p`` its softmax
@@ -336,6 +459,13 @@ def register_routed_toy():
         def norm(name):
             return PartSpec("rmsnorm", dict(name=name, hidden_size=config.hidden_size, eps=config.eps))
 
+        def position(i):
+            # The last layer encodes positions by learned offsets, the others by squashed rotation.
+            if i == config.num_hidden_layers - 1:
+                return PartSpec("learned_offset", dict(prefix=f"layers.{i}.attn.", head_dim=config.head_dim,
+                                                       max_positions=config.max_position_embeddings))
+            return PartSpec("squashed_rotary", dict(head_dim=config.head_dim, theta=config.theta, factor=4.0))
+
         def feed_forward(i):
             kind = "two_experts" if i % 2 else "swiglu"
             return PartSpec(kind, dict(prefix=f"layers.{i}.mlp.", hidden_size=config.hidden_size, intermediate_size=config.intermediate_size))
@@ -344,8 +474,7 @@ def register_routed_toy():
             PartSpec("pre_norm_residual", dict(
                 mixer=PartSpec("gqa_attention", dict(
                     prefix=f"layers.{i}.attn.", hidden_size=config.hidden_size, q_heads=config.heads, kv_heads=config.kv_heads,
-                    head_dim=config.head_dim, qkv_bias=False,
-                    position=PartSpec("squashed_rotary", dict(head_dim=config.head_dim, theta=config.theta, factor=4.0)))),
+                    head_dim=config.head_dim, qkv_bias=False, position=position(i))),
                 feed_forward=feed_forward(i), mixer_norm=norm(f"layers.{i}.norm1"), feed_forward_norm=norm(f"layers.{i}.norm2")))
             for i in range(config.num_hidden_layers)
         ]
@@ -358,6 +487,7 @@ def register_routed_toy():
             head=PartSpec("linear_head", dict(name="head", vocab_size=config.vocab_size, hidden_size=config.hidden_size)))
 
     register_part("position", "squashed_rotary", SquashedRotary, replace=True)
+    register_part("position", "learned_offset", LearnedOffset, replace=True)
     register_part("feed_forward", "two_experts", TwoExperts, replace=True)
     register_architecture("ToyRoutedForCausalLM", RoutedConfig.from_json_dict, recipe, replace=True)
     return RoutedConfig
@@ -373,7 +503,11 @@ def routed_plain(config, weights, tokens):
         q = plain.linear(h, weights[p + "attn.q_proj.weight"]).reshape(len(tokens), heads, d)
         k = plain.linear(h, weights[p + "attn.k_proj.weight"]).reshape(len(tokens), kv_heads, d)
         v = plain.linear(h, weights[p + "attn.v_proj.weight"]).reshape(len(tokens), kv_heads, d)
-        q, k = plain.rope(q, positions, config["theta"]), plain.rope(k, positions, config["theta"])
+        if i == config["num_hidden_layers"] - 1:
+            offset = weights[p + "attn.position_offset.weight"][: len(tokens), None, :]
+            q, k = q + offset, k + offset
+        else:
+            q, k = plain.rope(q, positions, config["theta"]), plain.rope(k, positions, config["theta"])
         x = x + plain.linear(plain.attention(q, k, v, d**-0.5), weights[p + "attn.o_proj.weight"])
         h = plain.rms_norm(x, weights[p + "norm2.weight"], config["eps"])
         if i % 2:
