@@ -36,6 +36,11 @@ def main(argv: list[str] | None = None) -> int:
     )
     parser.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE, help="tokens per cache page (divides 64)")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument(
+        "--kernels", choices=["tuned", "plain"], default="tuned",
+        help="'plain': the plain attention kernel and the library's matrix products in every step, as the "
+        "engine's kernels='plain' (what the tuned kernels are checked against)",
+    )
     args = parser.parse_args(argv)
     if args.max_tokens <= 0:
         parser.error("--max-tokens must be positive")
@@ -66,7 +71,8 @@ def main(argv: list[str] | None = None) -> int:
         step_tokens=pool_tokens,
         num_pages=pool_tokens // args.page_size,
     )
-    runner = ModelRunner(model, cache, max_batch_tokens=pool_tokens)
+    options = {"attention": "plain", "gemm": "library"} if args.kernels == "plain" else {}
+    runner = ModelRunner(model, cache, max_batch_tokens=pool_tokens, options=options)
     ids: dict[str, int] = {}
     next_id = 1
 

@@ -346,3 +346,131 @@ def test_a_failing_step_cancels_its_requests_and_the_engine_goes_on(tiny, where)
         setattr(target, attribute, original)
         assert engine.stats()["cancelled"] == before + 1 and not engine.has_work() and drained(engine)
         assert engine.generate(prompts[2], 5) == plain.greedy(config, weights, prompts[2], 5)
+
+
+# --- the scheduler's path over the tensor-core kernels ---------------------------------------------
+#
+# The tiny configurations have heads of 16 and 32, which in bfloat16 run the plain attention
+# kernel. These two models have heads of 128 and 64 and pages of 64: their prompt portions run the
+# tcgen05 (or mma.sync) prefill kernel, their decode steps the split-key kernels fed by TMA (or
+# cp.async), replayed from captured graphs and launched ahead of the host. Queries and keys are
+# scaled up so that attention picks few keys and a wrong one changes the greedy token.
+
+
+@pytest.fixture(scope="module", params=["heads_of_128", "heads_of_64"])
+def heads(request, tmp_path_factory):
+    from helpers import OTHER_SIZES, SHARPENED, sharpen_attention
+
+    name = request.param
+    folder = make_model_folder(tmp_path_factory.mktemp(name), OTHER_SIZES[name], seed=41)
+    sharpen_attention(folder, SHARPENED[name])
+    config, weights = plain_weights(folder)
+    return name, folder, config, weights
+
+
+def heads_engine(folder, **options):
+    from llm_inference_b200 import create_engine
+
+    settings = dict(max_num_sequences=4, kv_cache_bytes=8 << 20, prefill_chunk_size=48, prefill_burst_size=96, dtype="bfloat16")
+    settings.update(options)
+    return create_engine(folder, **settings)
+
+
+def follows_plain_until_a_near_tie(config, weights, prompt, got, what) -> int:
+    """Every token is the plain implementation's greedy pick, up to the first place where the
+    plain logits of the two picks lie within bfloat16's reach of each other; returns how many
+    tokens were checked."""
+    tokens = list(prompt)
+    for step, token in enumerate(got):
+        logits = plain.forward(config, weights, tokens)[-1]
+        best = int(np.argmax(logits))
+        if token != best:
+            assert logits[best] - logits[token] <= 2 * TOLERANCE["bfloat16"], f"{what}: step {step}"
+            return step
+        tokens.append(token)
+    return len(got)
+
+
+def test_scheduler_over_the_tensor_core_kernels_follows_plain(heads):
+    name, folder, config, weights = heads
+    rng = np.random.default_rng(5)
+    prompts = [random_tokens(rng, config["vocab_size"], n) for n in (150, 70, 97, 201)]
+    with heads_engine(folder) as engine:
+        alone = [engine.generate(p, 20) for p in prompts]
+        together = run_all(engine, prompts, 20)
+        stats = engine.stats()
+        assert drained(engine)
+    assert engine.runner.graph_replays > 20 and stats["steps_ahead_used"] > 20
+    checked = [follows_plain_until_a_near_tie(config, weights, p, out, f"{name} alone {i}") for i, (p, out) in enumerate(zip(prompts, alone))]
+    assert sum(checked) >= 40, checked  # most tokens are decided well clear of a tie
+    for i, (p, out) in enumerate(zip(prompts, together)):
+        follows_plain_until_a_near_tie(config, weights, p, out, f"{name} together {i}")
+    # Batched beside other requests or alone: the same kernels at other batch sizes; the tokens
+    # agree until a near-tie (equality across batch sizes is to rounding, not to the bit).
+    for p, a, b in zip(prompts, alone, together):
+        if a != b:
+            first = next(i for i, (x, y) in enumerate(zip(a, b)) if x != y)
+            logits = plain.forward(config, weights, list(p) + a[:first])[-1]
+            assert abs(logits[a[first]] - logits[b[first]]) <= 2 * TOLERANCE["bfloat16"]
+
+
+def test_run_ahead_over_the_tensor_core_kernels_changes_nothing(heads):
+    """The run-ahead scenario (a stop token, a cancel, a late submit, a forced token) at heads of
+    128 and 64: the same tokens with and without steps launched ahead."""
+    name, folder, config, weights = heads
+    rng = np.random.default_rng(6)
+    prompts = [random_tokens(rng, config["vocab_size"], n) for n in (90, 130, 65, 77)]
+    with heads_engine(folder, run_ahead=False) as engine:
+        long = engine.generate(prompts[0], 40)
+    stop = long[17]
+
+    def scenario(run_ahead: bool):
+        with heads_engine(folder, run_ahead=run_ahead) as engine:
+            a = engine.submit(prompts[0], 40, [stop])
+            b = engine.submit(prompts[1], 33)
+            c = engine.submit(prompts[2], 50)
+            steps, late = 0, None
+            while engine.has_work():
+                engine.step()
+                steps += 1
+                if steps == 12:
+                    engine.cancel(c)
+                if steps == 20:
+                    late = engine.submit(prompts[3], 14)
+                if steps == 25:
+                    engine.force(b, [1])
+            outputs = [list(engine.request(r).output) for r in (a, b, c, late)]
+            stats = engine.stats()
+            assert drained(engine)
+        return outputs, stats
+
+    with_ahead, stats = scenario(True)
+    without, _ = scenario(False)
+    assert with_ahead == without
+    assert stats["steps_ahead_used"] > 10 and stats["steps_ahead_dropped"] >= 1
+    assert with_ahead[0] == long[: long.index(stop) + 1]
+    follows_plain_until_a_near_tie(config, weights, prompts[3], with_ahead[3], f"{name} late request")
+
+
+def test_pages_with_non_finite_leftovers_are_harmless(heads):
+    """Pages go from request to request without being cleared, and the tensor-core attention
+    kernels load whole tiles of a page, masking rows past a request's last key only in the
+    scores. Here every page is filled with NaN between two runs of the same request: the
+    token that starts a page clears the rows its request has not written yet, so the second
+    run gives the first run's tokens and logits (prefill, then decode steps from graphs)."""
+    import torch
+
+    name, folder, config, weights = heads
+    prompt = random_tokens(np.random.default_rng(7), config["vocab_size"], 150)
+    with heads_engine(folder) as engine:
+        first_logits = engine.prefill_logits(prompt)
+        first = engine.generate(prompt, 12)
+        assert drained(engine)
+        torch.cuda.synchronize()
+        for group in engine.cache.groups:
+            group.arena[:, :, : group.capacity_pages].fill_(float("nan"))  # all but the spare page of padded rows
+        again_logits = engine.prefill_logits(prompt)
+        again = engine.generate(prompt, 12)
+    assert np.isfinite(again_logits).all()
+    assert np.array_equal(first_logits, again_logits) and first == again
+    follows_plain_until_a_near_tie(config, weights, prompt, first, f"{name} after NaN pages")

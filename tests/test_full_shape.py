@@ -1,8 +1,9 @@
 """Layers of the benchmark's size (Qwen2.5-1.5B: 12/2 heads of 128, hidden 1536, intermediate
 8960, vocabulary 151936), three of them with random weights: a 700-token prompt in two
-portions and three decoded tokens, in bfloat16 with each attention kernel, against the 32-bit
-path. The tiny test configurations never reach the tile counts, cluster sizes and split
-factors these sizes do."""
+portions and three decoded tokens. First the 32-bit path against the plain implementation
+(and the same for two layers of the 7B and 14B sizes), then bfloat16 with each attention
+kernel against the 32-bit path. The tiny test configurations never reach the tile counts,
+cluster sizes and split factors these sizes do."""
 
 from __future__ import annotations
 
@@ -47,6 +48,48 @@ def logits_of(dtype: str, attention: str, window: int, gemm: str = "auto", shape
     out = torch.cat(rows).float().cpu().numpy()
     engine.close()
     return out
+
+
+PROMPT_SEED, PROMPT_LENGTH, FIRST_PORTION, DECODED = 0, 700, 517, (11, 222, 3333)
+
+
+def plain_logits(shape: dict, window: int = 0) -> np.ndarray:
+    """What `logits_of` returns, from the plain implementation: the same seeded weights (drawn on
+    the GPU as bfloat16, handed over tensor by tensor), the whole sequence at once, logits at the
+    five places the engine is asked for."""
+    from helpers import device_model
+    from plain import qwen2_plain as plain
+
+    settings = dict(shape, use_sliding_window=window > 0, sliding_window=window if window else 32768)
+    _, config, weights = device_model(settings, seed=5, dtype=None, std=0.05)
+    prompt = [int(t) for t in np.random.default_rng(PROMPT_SEED).integers(0, settings["vocab_size"], PROMPT_LENGTH)]
+    tokens = prompt + list(DECODED)
+    hidden = plain.hidden_states(config, weights, tokens)
+    rows = [FIRST_PORTION - 1, PROMPT_LENGTH - 1, PROMPT_LENGTH, PROMPT_LENGTH + 1, PROMPT_LENGTH + 2]
+    return plain.output_logits(config, weights, hidden[rows])
+
+
+def test_32_bit_path_at_benchmark_sizes_matches_plain():
+    """The float32 path (own FMA products over inner sizes up to 18,944, plain attention over 700
+    keys) against the plain float64 implementation: within a thousandth of the logits' range."""
+    import gc
+
+    import torch
+
+    for name, shape in {"1.5B": SHAPE, **LARGER}.items():
+        want = plain_logits(shape)
+        got = logits_of("float32", "auto", 0, shape=shape)
+        span = float(want.max() - want.min())
+        error = np.abs(got - want)
+        assert error.max() <= 1e-3 * span, (name, error.max(), span)
+        assert (got.argmax(axis=1) == want.argmax(axis=1)).all(), name
+        print(f"{name}: float32 path max |logit error| {error.max():.3e}, logits' range {span:.2f}")
+        gc.collect()
+        torch.cuda.empty_cache()
+    # A window that ends inside the prompt, on the 1.5B size.
+    want = plain_logits(SHAPE, window=300)
+    got = logits_of("float32", "auto", 300)
+    assert np.abs(got - want).max() <= 1e-3 * float(want.max() - want.min())
 
 
 def assert_same_greedy_tokens(got: np.ndarray, reference: np.ndarray, name: str = "") -> None:
