@@ -173,6 +173,8 @@ def main() -> int:
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens each request holds before it decodes")
     parser.add_argument("--context", type=int, default=0, help="longest request the engine is built for (default: twice the prompt)")
     parser.add_argument("--no-graphs", action="store_true")
+    parser.add_argument("--decode-kernel", choices=["chain", "resident"], default="chain",
+                        help="'resident': time the one-kernel decode step instead of the chain of kernels")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -230,7 +232,7 @@ def main() -> int:
     engine = Engine(
         model=model, max_num_sequences=max_batch, max_model_length=context, kv_cache_bytes=budget_tokens * kv_bytes_per_token,
         page_size=PAGE, prefill_chunk_size=PROMPT, prefill_burst_size=PROMPT, max_batch_tokens=PROMPT + max_batch,
-        cuda_graphs=not args.no_graphs,
+        cuda_graphs=not args.no_graphs, decode_kernel=args.decode_kernel,
     )
     runner, cache = engine.runner, engine.cache
     rng = np.random.default_rng(0)
@@ -388,6 +390,7 @@ def main() -> int:
             "page_size": PAGE,
             "parallelism": "single GPU",
             "cuda_graphs": not args.no_graphs,
+            "decode_kernel": args.decode_kernel,
             "l2": "inputs larger than L2: each step reads all weights (GBs)",
             "peaks": peak["source"],
         },

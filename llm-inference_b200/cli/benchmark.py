@@ -147,7 +147,7 @@ def main(argv=None) -> int:
             "tpot_ms": percentiles([m["tpot_ms"] for m in all_metrics if m["tpot_ms"] is not None]),
             "e2e_ms": percentiles([m["e2e_ms"] for m in all_metrics]),
         },
-        "engine_stats": {k: v for k, v in stats.items() if not isinstance(v, dict)},
+        "engine_stats": {k: v for k, v in stats.items() if not isinstance(v, dict) or k == "step_timing"},
         "requests": all_metrics,
     }
     args.output.parent.mkdir(parents=True, exist_ok=True)

@@ -29,6 +29,9 @@ def add_engine_options(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--prefill-burst-size", type=int, default=2048)
     parser.add_argument("--no-cuda-graphs", action="store_true")
     parser.add_argument("--kernels", choices=["tuned", "plain"], default="tuned")
+    parser.add_argument("--decode-kernel", choices=["chain", "resident"], default="chain",
+                        help="'resident': decode steps of up to 16 requests as one resident kernel (slower; an option)")
+    parser.add_argument("--step-timing", action="store_true", help="measure host and device time of every model step (reported in the engine's stats)")
     parser.add_argument("--nvtx", action="store_true", help="name NVTX ranges (step, layer N, head, sample) for a profiler's timeline")
     parser.add_argument("--no-run-ahead", action="store_true", help="never launch a decode step before the previous one was read back")
 
@@ -40,7 +43,7 @@ def engine_from(args):
         dtype=args.dtype, max_num_sequences=args.max_sequences, max_model_length=args.max_model_length,
         kv_cache_bytes=args.kv_cache_mib << 20, page_size=args.page_size, prefill_chunk_size=args.prefill_chunk_size,
         prefill_burst_size=max(args.prefill_burst_size, args.prefill_chunk_size), cuda_graphs=not args.no_cuda_graphs,
-        run_ahead=not args.no_run_ahead, kernels=args.kernels, nvtx=args.nvtx,
+        run_ahead=not args.no_run_ahead, kernels=args.kernels, decode_kernel=args.decode_kernel, nvtx=args.nvtx, step_timing=args.step_timing,
     )
     if (args.model is None) == (args.random is None):
         raise SystemExit("give either --model DIR or --random SHAPE")

@@ -183,9 +183,64 @@ def bench_attention(args, decode: bool) -> dict:
             "layers": args.layers, "us": us, "GBps": kv_bytes / us / 1e3, "TFLOPs": flops / us / 1e6}
 
 
+def bench_resident(args) -> dict:
+    """One decode step as the resident kernel at a named shape: time per step, and for each kind of
+    phase how long the slowest block takes to ask for its operand, to finish, and how long block 0
+    then waits at the barrier (timestamps the kernel records when handed a trace buffer)."""
+    import numpy as np
+
+    from .. import models  # noqa: F401
+    from ..config import parse_config
+    from ..engine.engine import Engine
+    from ..engine.loading import random_model
+    from ..engine.runner import StepEntry
+    from .presets import PRESETS
+
+    _, config = parse_config(dict(PRESETS[args.shape]))
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    engine = Engine(model=model, max_num_sequences=16, max_model_length=2 * args.context, kv_cache_bytes=8 << 30,
+                    prefill_chunk_size=2048, prefill_burst_size=2048, max_batch_tokens=2048 + 16, cuda_graphs=False,
+                    decode_kernel="resident")
+    runner = engine.runner
+    if runner.options["resident"] is None:
+        raise SystemExit("the resident kernel does not take this shape")
+    rng = np.random.default_rng(0)
+    ids = list(range(1, args.batch + 1))
+    for rid in ids:
+        engine.cache.open(rid)
+        for begin in range(0, args.context, 2048):
+            runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, config.vocab_size, min(2048, args.context - begin))], ())])
+    phases = 2 + 5 * len(model.schedule)
+    trace = torch.zeros(phases * 4, dtype=torch.int64, device="cuda")
+    runner.options["resident_trace"] = trace
+    step = lambda: runner.step([StepEntry(rid, (int(rng.integers(0, config.vocab_size)),), (0,)) for rid in ids])
+    for _ in range(3):
+        step()
+    trace.zero_()
+    us = time_launches(step, args.iters)
+    trace.zero_()
+    step()
+    torch.cuda.synchronize()
+    runner.check()
+    stamps = trace.cpu().numpy().reshape(phases, 4).astype(np.float64) / 1e3
+    names = ["embedding"] + ["q/k/v", "attention", "output", "gate/up", "down"] * len(model.schedule) + ["head"]
+    kinds: dict[str, list] = {}
+    for name, (enter, asked, finished, left) in zip(names, stamps):
+        asked = asked if asked > 0 else enter
+        kinds.setdefault(name, []).append((asked - enter, finished - asked, max(left - finished, 0.0) if left > 0 else 0.0))
+    summary = {
+        name: dict(zip(("operand_asked_us", "work_us", "barrier_us"), (round(float(v), 2) for v in np.mean(rows, axis=0))))
+        for name, rows in kinds.items()
+    }
+    engine.close()
+    return {"kernel": "resident_decode", "shape": args.shape, "batch": args.batch, "context": args.context, "us_per_step": us,
+            "kernel_us": float(stamps[-1, 2] - stamps[0, 0]), "phases": summary}
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention"])
+    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident"])
+    parser.add_argument("--shape", default="qwen2.5-1.5b", help="resident: a named model shape")
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=17920)
     parser.add_argument("--k", type=int, default=1536)
@@ -216,6 +271,8 @@ def main(argv=None) -> int:
         args.gemm = "library"
     if args.kernel == "gemm":
         result = bench_gemm(args)
+    elif args.kernel == "resident":
+        result = bench_resident(args)
     else:
         result = bench_attention(args, args.kernel == "decode_attention")
     print(json.dumps(result))

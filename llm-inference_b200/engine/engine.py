@@ -100,11 +100,15 @@ class Engine:
         cuda_graphs: bool = True,
         run_ahead: bool = True,
         kernels: str = "tuned",
+        decode_kernel: str = "chain",
         nvtx: bool = False,
+        step_timing: bool = False,
         model: Model | None = None,
     ) -> None:
         if kernels not in ("tuned", "plain"):
             raise ValueError(f"kernels={kernels!r}; expected 'tuned' or 'plain'")
+        if decode_kernel not in ("chain", "resident"):
+            raise ValueError(f"decode_kernel={decode_kernel!r}; expected 'chain' or 'resident'")
         if max_num_sequences <= 0 or kv_cache_bytes <= 0 or page_size <= 0:
             raise ValueError("sequences, cache bytes and page size must be positive")
         if not 0 < prefill_chunk_size <= prefill_burst_size:
@@ -150,6 +154,10 @@ class Engine:
             # slow, simple kernels the tuned ones are checked against); "tuned": each step's best.
             options={
                 "cuda_graphs": cuda_graphs, "workspace_rows": self.max_batch_tokens, "nvtx": bool(nvtx),
+                # "chain": every step is a chain of kernels; "resident": decode steps of up to 16
+                # requests as one resident kernel where the model allows it (slower; kept as an option).
+                "decode_kernel": "chain" if kernels == "plain" else decode_kernel,
+                "step_timing": bool(step_timing),
                 **({"attention": "plain", "gemm": "library"} if kernels == "plain" else {}),
             },
         )
@@ -359,6 +367,11 @@ class Engine:
         }
         out.update(self.scheduler.stats())
         out.update(self.cache.stats())
+        if self.runner.step_timing:
+            # Where a step's time goes: the host inside the step function against the device's time
+            # for the same steps (steps launched ahead of the host are not among them).
+            timing = self.runner.timing()
+            out["step_timing"] = timing
         return out
 
     def build_info(self) -> dict[str, object]:

@@ -14,6 +14,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Sequence
 
+import time
+
 import numpy as np
 import torch
 
@@ -127,11 +129,26 @@ class ModelRunner:
         self.tokens_run = 0
         # Decode-only steps replay a CUDA graph per batch-size bucket (see _decode_graph).
         self.use_graphs = bool(self.options.get("cuda_graphs", True)) and bool(getattr(model, "graph_safe", False))
+        # With options["decode_kernel"] = "resident", steps of up to 16 single tokens run as one
+        # resident kernel when the model is made of the parts that kernel was written for. The
+        # default is the chain of kernels, which is the faster of the two (see parts/resident.py).
+        self.options["resident"] = None
+        if self.options.get("decode_kernel", "chain") == "resident":
+            from ..parts.resident import ResidentDecoder
+
+            self.options["resident"] = ResidentDecoder.for_model(model, cache, self.lib)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_generation = -1
         self.graph_replays = 0
         self.launches_per_graph: dict[int, int] = {}
         self.issue = 0  # batches launched so far; an AheadStep is only good while nothing followed it
+        # With options["step_timing"]: the host's wall time inside `step` and, from two events per
+        # step that are read only when asked for, the device's time for the same steps.
+        self.step_timing = bool(self.options.get("step_timing"))
+        self.host_seconds = 0.0
+        self._device_ms = 0.0
+        self._timed_steps = 0
+        self._open_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
 
     # ------------------------------------------------------------------------------------------
 
@@ -143,6 +160,31 @@ class ModelRunner:
         manager = self.cache.manager
         if not entries:
             return torch.empty((0, self.model.head.vocab_size), dtype=torch.float32, device=self.device)
+        if self.step_timing:
+            began = time.perf_counter()
+            events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            events[0].record()
+            try:
+                return self._step(entries, check)
+            finally:
+                events[1].record()
+                self._open_events.append(events)
+                self._timed_steps += 1
+                self.host_seconds += time.perf_counter() - began
+        return self._step(entries, check)
+
+    def timing(self) -> dict[str, float]:
+        """Totals over the steps run with ``step_timing``: the host's time inside `step`
+        (building metadata and launching) and the device's time between each step's first
+        and last launch. Reading the device's time waits for the steps to finish."""
+        for first, last in self._open_events:
+            last.synchronize()
+            self._device_ms += first.elapsed_time(last)
+        self._open_events.clear()
+        return {"timed_steps": self._timed_steps, "host_ms": self.host_seconds * 1e3, "device_ms": self._device_ms}
+
+    def _step(self, entries: Sequence[StepEntry], check: bool) -> torch.Tensor:
+        manager = self.cache.manager
         seen = set()
         for e in entries:
             if e.request_id in seen:

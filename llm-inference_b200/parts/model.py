@@ -140,6 +140,12 @@ class Model:
         # marks them (cuda/qwen_model.cu:106,138,169); the ranges are host-side marks around the
         # launches and change nothing on the device.
         mark = _nvtx_range if ctx.options.get("nvtx") else _no_range
+        # A step of single tokens of a model made of the stock parts can run as one resident
+        # kernel (parts/resident.py) instead of the chain of kernels below.
+        resident = ctx.options.get("resident")
+        if resident is not None and resident.takes(ctx):
+            with mark("resident step"):
+                return resident.run(ctx, cache_views)
         x = self.embedding.forward(ctx)
         delta = None
         for call in self.schedule:
