@@ -132,13 +132,134 @@ class ClockSampler:
         }
 
 
-def reference_arm() -> int:
-    reason = (
-        "the reference does not install offline here: pip finds no numpy wheel for its dependency, and with "
-        "--no-deps its CMake build fails (CUDA::nvToolsExt is not in CUDA 12.9); its only engine that has "
-        "ever run needs MLX on Apple hardware"
+REFERENCE_DIR = ROOT / "baseline" / "_ref"
+REFERENCE_CONTEXT = 2048  # the longest request the reference's CUDA engine takes (cuda/qwen_model.cu:60-61)
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference, installed offline into baseline/_ref, through its own public API
+    (``instinct.create_engine(path, backend="cuda")``, ``submit`` / ``step``): the same model shape with
+    seeded random weights written by its own ``write_engine``, the same batch, greedy decoding.
+    Its CUDA engine refuses requests longer than 2,048 tokens, so the prompts are 1,024 tokens
+    where the headline configuration has 2,048 (``same_config`` is false in the line)."""
+
+    def unavailable(reason: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+        return 0
+
+    if args.gpus != 1:
+        return unavailable("the reference's CUDA engine runs on one GPU")
+    if not (REFERENCE_DIR / "instinct").is_dir():
+        return unavailable(
+            "the reference is not installed under baseline/_ref (offline install: pip --no-deps from a writable copy, "
+            "with the CMake target CUDA::nvToolsExt supplied by baseline/nvtx_shim; see DESIGN.md)"
+        )
+    sys.path.insert(0, str(REFERENCE_DIR))
+    try:
+        import numpy as np
+        import torch
+
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device is visible")
+        import instinct
+        from instinct.format import ModelConfig, write_engine
+
+        if instinct.CudaEngine is None:
+            return unavailable("the reference's CUDA extension did not import")
+    except Exception as error:  # noqa: BLE001 (whatever stops the import is the reason)
+        return unavailable(f"importing the reference failed: {type(error).__name__}: {error}")
+
+    import tempfile
+
+    shape = MODEL
+    if args.model != "qwen2.5-1.5b":
+        return unavailable("the reference arm is set up for the headline shape only")
+    batch, steps, warmup = args.batch, args.steps, max(3, args.warmup)
+    prompt_len = min(args.prompt_len, REFERENCE_CONTEXT // 2)
+    new_tokens = REFERENCE_CONTEXT - prompt_len
+    rng = np.random.default_rng(0)
+    hidden, inter, layers = shape["hidden_size"], shape["intermediate_size"], shape["num_hidden_layers"]
+    heads, kv_heads, vocab = shape["num_attention_heads"], shape["num_key_value_heads"], shape["vocab_size"]
+    head_dim = hidden // heads
+
+    def draw(*dims, mean=0.0):
+        return (mean + 0.02 * rng.standard_normal(dims, dtype=np.float32)).astype(np.float16)
+
+    tensors = {"model.embed_tokens.weight": draw(vocab, hidden), "model.norm.weight": draw(hidden, mean=1.0)}
+    for layer in range(layers):
+        p = f"model.layers.{layer}."
+        tensors[p + "input_layernorm.weight"] = draw(hidden, mean=1.0)
+        tensors[p + "post_attention_layernorm.weight"] = draw(hidden, mean=1.0)
+        for name, rows in (("q_proj", heads * head_dim), ("k_proj", kv_heads * head_dim), ("v_proj", kv_heads * head_dim)):
+            tensors[p + f"self_attn.{name}.weight"] = draw(rows, hidden)
+            tensors[p + f"self_attn.{name}.bias"] = draw(rows)
+        tensors[p + "self_attn.o_proj.weight"] = draw(hidden, heads * head_dim)
+        tensors[p + "mlp.gate_proj.weight"] = draw(inter, hidden)
+        tensors[p + "mlp.up_proj.weight"] = draw(inter, hidden)
+        tensors[p + "mlp.down_proj.weight"] = draw(hidden, inter)
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"]
+    config = ModelConfig(
+        vocab_size=vocab, hidden_size=hidden, intermediate_size=inter, num_hidden_layers=layers,
+        num_attention_heads=heads, num_key_value_heads=kv_heads, max_position_embeddings=shape["max_position_embeddings"],
+        eos_token_id=int(shape["eos_token_id"]), rope_theta=float(shape["rope_theta"]), rms_norm_eps=float(shape["rms_norm_eps"]),
     )
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            path = Path(tmp) / "model.engine"
+            write_engine(path, config, tensors, aliases={"lm_head.weight": "model.embed_tokens.weight"})
+            del tensors
+            kv_bytes = batch * REFERENCE_CONTEXT * 2 * layers * kv_heads * head_dim * 2 + (64 << 20)
+            engine = instinct.create_engine(
+                path, backend="cuda", max_num_sequences=batch, max_model_length=REFERENCE_CONTEXT, kv_cache_bytes=kv_bytes
+            )
+            # Prefill of one prompt of the engine's longest length, timed through its own API.
+            long_prompt = [int(t) for t in rng.integers(0, vocab, REFERENCE_CONTEXT - 1)]
+            engine.generate(long_prompt[:64], 1, [])  # first use: cuBLASLt plans, module load
+            begin = time.perf_counter()
+            engine.generate(long_prompt, 1, [])
+            prefill_s = time.perf_counter() - begin
+            ids = [engine.submit([int(t) for t in rng.integers(0, vocab, prompt_len)], new_tokens, []) for _ in range(batch)]
+            for _ in range(batch):  # it prefills one waiting request per step
+                engine.step()
+            for _ in range(warmup):
+                engine.step()
+            sampler = ClockSampler()
+            sampler.start()
+            torch.cuda.synchronize()
+            mark = sampler.mark()
+            begin = time.perf_counter()
+            emitted, timed = 0, 0
+            room = new_tokens - batch - warmup - 2
+            while timed < steps or (time.perf_counter() - begin < MIN_TIMED_S and timed + steps <= room):
+                for _ in range(steps):
+                    emitted += len(engine.step())  # synchronises its stream; tokens come back to the host
+                timed += steps
+            elapsed = time.perf_counter() - begin
+            clocks = sampler.summary(mark, sampler.mark())
+            sampler.stop()
+            for rid in ids:
+                engine.cancel(rid)
+    except Exception as error:  # noqa: BLE001
+        return unavailable(f"the reference's CUDA engine failed: {type(error).__name__}: {error}")
+    value = emitted / elapsed
+    line = {
+        "metric": f"decode tok/s (batch {batch}, {prompt_len:,}-token prompts, Qwen2.5-1.5B shape)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": elapsed / timed * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+        "data": "synthetic: seeded random weights N(0,0.02), token ids uniform in the vocabulary",
+        "impl": "reference", "same_config": False,
+        "config": {
+            "model": "Qwen2.5-1.5B shape", "layers": layers, "layers_full": layers, "hidden": hidden, "q_heads": heads,
+            "kv_heads": kv_heads, "head_dim": head_dim, "intermediate": inter, "vocab": vocab, "tied_head": True,
+            "global_batch": batch, "seq_len": REFERENCE_CONTEXT, "prompt_len": prompt_len, "parallelism": "single GPU",
+            "why_not_same": "the reference's CUDA engine takes at most 2,048 tokens per request",
+            "timing": "host clock around its Engine.step, which synchronises every step",
+        },
+        "e2e": {"value": value, "unit": "tokens/s", "steps": timed},
+        "prefill": {"value": (REFERENCE_CONTEXT - 1) / prefill_s, "tokens": REFERENCE_CONTEXT - 1, "ms": prefill_s * 1e3},
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
     return 0
 
 
@@ -177,7 +298,7 @@ def main() -> int:
                         help="'resident': time the one-kernel decode step instead of the chain of kernels")
     args = parser.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -137,7 +137,7 @@ class ModelRunner:
             from ..parts.resident import ResidentDecoder
 
             self.options["resident"] = ResidentDecoder.for_model(model, cache, self.lib)
-        self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
+        self._graphs: dict[tuple[int, int], tuple[torch.cuda.CUDAGraph, torch.Tensor, int]] = {}
         self._graph_generation = -1
         self.graph_replays = 0
         self.launches_per_graph: dict[int, int] = {}
@@ -265,16 +265,17 @@ class ModelRunner:
         if not self.use_graphs or count == 0 or count > self.cache.max_num_sequences:
             return None
         bucket = self._bucket(count)
-        cached = self._graphs.get(bucket)
-        if cached is None or self._graph_generation != self.workspace.generation:
-            return None
         manager = self.cache.manager
         starts = [manager.length(r) for r in request_ids]
         if any(start + 1 > self.cache.max_pages_per_request * self.cache.page_size for start in starts):
             return None
+        reach = self._reach(max(starts) + 1)
+        cached = self._graphs.get((bucket, reach))
+        if cached is None or self._graph_generation != self.workspace.generation:
+            return None
         for r, start in zip(request_ids, starts):
             manager.ensure(r, start + 1)
-        self._build_context([StepEntry(r, (0,)) for r in request_ids], starts, list(range(bucket)), pad_to=bucket)
+        self._build_context([StepEntry(r, (0,)) for r in request_ids], starts, list(range(bucket)), pad_to=bucket, reach=reach)
         self.staging.dev[:count].copy_(tokens_dev[:count], non_blocking=True)  # the token ids lead the buffer
         graph, logits, _ = cached
         graph.replay()
@@ -318,14 +319,26 @@ class ModelRunner:
             bucket *= 2
         return min(bucket, max(self.cache.max_num_sequences, count))
 
+    def _reach(self, longest: int) -> int:
+        """The key count a captured step is launched for: the next power of two (from 1,024 on) at
+        or above the longest request of the step, at most the engine's limit. The kernels walk
+        each request's own keys whatever this is; it only decides how many blocks cut the keys, so
+        that an engine built for long requests does not launch its short ones in 64 pieces."""
+        limit = self.cache.max_pages_per_request * self.cache.page_size
+        reach = 1024
+        while reach < longest:
+            reach *= 2
+        return min(reach, limit)
+
     def _decode_graph(self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int]) -> torch.Tensor:
         count = len(entries)
         bucket = self._bucket(count)
+        reach = self._reach(max(starts) + 1)
         if self._graph_generation != self.workspace.generation:
             self._graphs.clear()  # a scratch buffer moved: captured addresses are stale
-        ctx = self._build_context(entries, starts, list(range(bucket)), pad_to=bucket)
+        ctx = self._build_context(entries, starts, list(range(bucket)), pad_to=bucket, reach=reach)
         tables = self._tables
-        cached = self._graphs.get(bucket)
+        cached = self._graphs.get((bucket, reach))
         if cached is None:
             calls_before = self.lib.calls
             learn = self.options.get("weight_prefetch", False) and "gemm_next" not in self.options
@@ -352,7 +365,7 @@ class ModelRunner:
                 torch.cuda.current_stream(self.device).synchronize()
                 with torch.cuda.graph(graph):
                     captured = self.model.forward(ctx, lambda call: self._view(call, tables))
-                self._graphs[bucket] = (graph, captured, self.workspace.generation)
+                self._graphs[(bucket, reach)] = (graph, captured, self.workspace.generation)
         else:
             graph, logits, _ = cached
             graph.replay()
@@ -362,7 +375,8 @@ class ModelRunner:
         return logits[torch.tensor(wanted_rows, dtype=torch.long, device=self.device)]
 
     def _build_context(
-        self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int], pad_to: int | None = None
+        self, entries: list[StepEntry], starts: list[int], wanted_rows: list[int], pad_to: int | None = None,
+        reach: int | None = None,
     ) -> StepContext:
         """Lay the step's metadata out in the pinned buffer, copy it to the device and wrap it.
         With ``pad_to`` (single-token steps only) the batch is filled up to that many requests
@@ -449,8 +463,9 @@ class ModelRunner:
             err=self.err,
             workspace=self.workspace,
             num_decode_seqs=decode,
-            # A captured step must launch for the longest request the engine allows.
-            max_kv_len=int(kv_len.max()) if pad_to is None else self.cache.max_pages_per_request * self.cache.page_size,
+            # A captured step is launched for a bucket of key counts (see _reach), not for this
+            # step's own longest request.
+            max_kv_len=int(kv_len.max()) if pad_to is None else (reach or self.cache.max_pages_per_request * self.cache.page_size),
             max_q_len=int(q_len.max()),
             captured=pad_to is not None,
             options=self.options,

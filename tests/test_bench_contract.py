@@ -32,7 +32,13 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert result.stdout.strip().count("\n") == 0 and "one GPU" in result.stdout
 
 
-def test_reference_arm_says_why_it_is_unavailable():
+def test_reference_arm_prints_one_line_and_says_why_when_it_cannot_run():
+    """Without a GPU (or without the reference installed under baseline/_ref) the arm prints one
+    line that says why and exits 0. Where it can run, that takes minutes and is the driver's job."""
+    import torch
+
+    if torch.cuda.is_available() and (ROOT / "baseline" / "_ref" / "instinct").is_dir():
+        pytest.skip("the reference is installed and a GPU is visible: the arm would run in full")
     result = run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
     assert result.returncode == 0
     line = json.loads(result.stdout.strip())
