@@ -79,6 +79,48 @@ __device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank
   return v;
 }
 
+// RMSNorm folded into the matrix products around it (decode steps of up to 16 tokens).
+//
+// A product whose input is a normalised residual stream may take, instead of the normalised
+// rows, the stream times the norm's scale (`xn`, bfloat16) and apply each token's 1 / rms to
+// its outputs afterwards: the factor commutes with the product. The sum of squares it needs
+// arrives as partial sums `ss_in[part][16]`, one row per block of the product that produced
+// the stream, added here in a fixed order. That producer is a product launched with the
+// second half of this struct: it adds its result into the 32-bit stream `x`, writes the
+// stream times the scale of the norm that FOLLOWS (`xn`) and its block's partial sums of
+// squares (`ss_out`). Either half, or both, may be unused (null pointers).
+struct NormFold {
+  const float* ss_in;   // [ss_parts][16]
+  int ss_parts;
+  int width;            // the stream's width: mean of squares = sum / width
+  float eps;
+  float* x;             // [M, N] residual stream, updated in place
+  const float* next_weight;  // [N] scale of the norm that follows
+  __nv_bfloat16* xn;    // [M, N]
+  float* ss_out;        // [parts of this launch][16]
+};
+constexpr int kFoldTokens = 16;  // row length of the partial sums
+
+// 1 / rms of token m from the partial sums, by one warp: each lane adds every 32nd part in
+// order, the lanes' sums meet in a fixed tree.
+__device__ __forceinline__ float fold_rstd(const NormFold& fold, int m) {
+  const int lane = threadIdx.x & 31;
+  float sum = 0.f;
+  for (int p0 = lane; p0 < fold.ss_parts; p0 += 32 * 4) {
+    float part[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = p0 + 32 * j;
+      part[j] = p < fold.ss_parts ? __ldcg(fold.ss_in + p * kFoldTokens + m) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sum += part[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  return rsqrtf(sum / static_cast<float>(fold.width) + fold.eps);
+}
+
 bool b200_overlap_enabled();
 int b200_sm_count_host();  // SMs of the current device (cached)
 

@@ -71,11 +71,12 @@ __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
                    void* __restrict__ Y, int M, int N, int K, int row_groups, int epilogue,
                    float* __restrict__ scratch, int* __restrict__ counters, const void* __restrict__ next_weights,
-                   long long next_bytes) {
+                   long long next_bytes, const NormFold fold) {
   // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* ring = reinterpret_cast<uint4*>(smem_raw);
   __shared__ int ticket_shared;
+  __shared__ float rstd_s[kFoldTokens];
   constexpr int kPieces = 2 + MT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -126,6 +127,14 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
 #pragma unroll
   for (int i = 0; i < kStages; ++i) fetch_x(c_begin + i, i);
   copy_async_commit();
+  if (fold.ss_in != nullptr) {
+    // The operand is the stream times a norm's scale: each token's 1 / rms, applied to the sums
+    // at the end. Two tokens per warp, while the first slabs are on their way.
+    for (int m = warp; m < M; m += kSkinnyWarps) {
+      const float r = fold_rstd(fold, m);
+      if (lane == 0) rstd_s[m] = r;
+    }
+  }
   copy_async_wait<0>();
 
   float acc[MT][4];
@@ -186,13 +195,42 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
   }
 
   const int block_n0 = blockIdx.x * block_rows;
+  const bool scaled = fold.ss_in != nullptr;
   auto total = [&](int r, int m) -> float {
-    if (sums == nullptr) return block_sum_at(partial, k_splits, block_rows, tokens_pad, r, m);
     float sum = 0.f;
-    for (int s = 0; s < static_cast<int>(gridDim.y); ++s)
-      sum += __ldcg(sums + static_cast<int64_t>(s) * tile + r * tokens_pad + m);
-    return sum;
+    if (sums == nullptr) {
+      sum = block_sum_at(partial, k_splits, block_rows, tokens_pad, r, m);
+    } else {
+      for (int s = 0; s < static_cast<int>(gridDim.y); ++s)
+        sum += __ldcg(sums + static_cast<int64_t>(s) * tile + r * tokens_pad + m);
+    }
+    return scaled ? sum * rstd_s[m] : sum;
   };
+  if (fold.x != nullptr) {
+    // The product goes into the residual stream; the stream times the next norm's scale and this
+    // block's partial sums of squares go out for the product that follows that norm.
+    __shared__ float squares[kFoldTokens * kSkinnyWarps * 16];  // [m][row of the block]
+    for (int item = threadIdx.x; item < M * block_rows; item += kSkinnyThreads) {
+      const int m = item / block_rows, r = item - m * block_rows;
+      const int n = block_n0 + r;
+      float sq = 0.f;
+      if (n < N) {
+        const int64_t at = static_cast<int64_t>(m) * N + n;
+        const float now = fold.x[at] + total(r, m);
+        fold.x[at] = now;
+        fold.xn[at] = __float2bfloat16_rn(now * fold.next_weight[n]);
+        sq = now * now;
+      }
+      squares[m * block_rows + r] = sq;
+    }
+    __syncthreads();
+    if (threadIdx.x < M) {
+      float sum = 0.f;
+      for (int r = 0; r < block_rows; ++r) sum += squares[threadIdx.x * block_rows + r];
+      fold.ss_out[static_cast<int64_t>(blockIdx.x) * kFoldTokens + threadIdx.x] = sum;
+    }
+    return;
+  }
   if (epilogue == EPI_SWIGLU) {
     const int pairs = block_rows / 2;
     for (int item = threadIdx.x; item < M * pairs; item += kSkinnyThreads) {
@@ -245,7 +283,8 @@ SkinnyPlan plan_skinny(int N, int K) {
 template <int MT>
 int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
                   const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
-                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false) {
+                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false,
+                  const NormFold& fold = NormFold{}) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
   const size_t ring = static_cast<size_t>(kSkinnyWarps) * SkinnyStages<MT>::value * (2 + MT) * 32 * 16;
@@ -265,7 +304,7 @@ int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M
   const dim3 grid(plan.blocks, plan.column_blocks);
   cudaError_t status = launch_kernel_as(ordered, skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X,
                                         Y, M, N, K, plan.row_groups, epilogue, scratch, counters, next_weights,
-                                        next_bytes);
+                                        next_bytes, fold);
   if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
   return 0;
 }
@@ -293,11 +332,53 @@ B200_API void b200_skinny_gemm_scratch(int M, int N, int K, int64_t* floats, int
   *counters = plan.column_blocks > 1 ? plan.blocks : 0;
 }
 
+// With a folded norm behind it (see NormFold): how many rows of partial sums of squares a launch
+// with the residual epilogue writes, one per block of rows.
+B200_API int b200_skinny_gemm_fold_parts(int N, int K) { return plan_skinny(N, K).blocks; }
+
+static int skinny_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, float* scratch,
+                           int64_t scratch_floats, int* counters, int num_counters, const void* next_weights,
+                           int64_t next_bytes, const NormFold& fold, cudaStream_t stream);
+
 // `next_weights` / `next_bytes` (may be null / 0): memory the kernel asks the L2 cache to fetch
 // while it runs, meant for the weights of the product that follows on the stream.
 B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
                               float* scratch, int64_t scratch_floats, int* counters, int num_counters,
                               const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
+  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, next_weights,
+                         next_bytes, NormFold{}, stream);
+}
+
+// The same product around a folded RMSNorm (NormFold in common.cuh). With `ss_in` the operand X is
+// the residual stream times the norm's scale and every token's outputs are multiplied by its
+// 1 / rms (any epilogue). With `x` the result is not written to Y (which may be null) but added
+// into the residual stream x[M, N]; xn and ss_out receive the stream times `next_weight` and
+// this launch's b200_skinny_gemm_fold_parts(N, K) rows of partial sums of squares (epilogue 0).
+B200_API int b200_skinny_gemm_fold(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
+                                   float* scratch, int64_t scratch_floats, int* counters, int num_counters,
+                                   const float* ss_in, int ss_parts, int width, float eps, float* x,
+                                   const float* next_weight, void* xn, float* ss_out, cudaStream_t stream) {
+  NormFold fold{};
+  fold.ss_in = ss_in;
+  fold.ss_parts = ss_parts;
+  fold.width = width;
+  fold.eps = eps;
+  fold.x = x;
+  fold.next_weight = next_weight;
+  fold.xn = static_cast<__nv_bfloat16*>(xn);
+  fold.ss_out = ss_out;
+  B200_REQUIRE(M <= kFoldTokens, "skinny_gemm_fold: at most %d tokens", kFoldTokens);
+  B200_REQUIRE(ss_in == nullptr || (ss_parts > 0 && width > 0), "skinny_gemm_fold: partial sums without their count");
+  B200_REQUIRE(x == nullptr || (next_weight != nullptr && xn != nullptr && ss_out != nullptr && epilogue == EPI_BF16),
+               "skinny_gemm_fold: the residual epilogue needs the next norm's scale, xn and ss_out");
+  B200_REQUIRE(x != nullptr || Y != nullptr, "skinny_gemm_fold: no output");
+  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, nullptr, 0, fold,
+                         stream);
+}
+
+static int skinny_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, float* scratch,
+                           int64_t scratch_floats, int* counters, int num_counters, const void* next_weights,
+                           int64_t next_bytes, const NormFold& fold, cudaStream_t stream) {
   B200_REQUIRE(b200_skinny_gemm_supported(M, N, K, epilogue), "skinny_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "skinny_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -311,8 +392,9 @@ B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int 
                static_cast<long long>(need_floats), need_counters);
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
-  if (M <= 8) return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes);
-  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes);
+  if (M <= 8)
+    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes, false, fold);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes, false, fold);
 }
 
 // ---- the variant that allocates nothing (declared and documented in gemm_skinny_static.h) ----

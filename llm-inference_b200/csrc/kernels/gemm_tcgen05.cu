@@ -139,6 +139,7 @@ struct StreamParams {
   int tokens_pad;  // MMA N: M rounded up to a multiple of 16
   int tmem_cols;   // power of two >= max(32, tokens_pad)
   int epilogue;
+  NormFold fold;   // RMSNorm folded into this product (common.cuh); all null when unused
 };
 
 __device__ __forceinline__ void write_output(const StreamParams& p, int m, int n, float v) {
@@ -160,6 +161,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_base_shared;
+  __shared__ float rstd_s[kFoldTokens];
+  __shared__ float squares[kFoldTokens * kBlockRows];  // [m][row of this member's slice]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
@@ -255,8 +258,18 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 
   // ---- epilogue: TMEM -> registers -> global, or -> shared memory when the cluster splits K ----
   float* partial = reinterpret_cast<float*>(tiles);  // [tokens_pad][128 rows]; the stages are idle by then
+  const bool scaled = p.fold.ss_in != nullptr;
   if (warp >= 2) {
     wait_for_predecessor();
+    if (scaled) {
+      // The operand is the stream times a norm's scale: each token's 1 / rms from the partial sums
+      // of squares, while the products run. Four tokens per epilogue warp.
+      for (int m = warp - 2; m < p.M; m += 4) {
+        const float r = fold_rstd(p.fold, m);
+        if (lane == 0) rstd_s[m] = r;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const int quarter = warp & 3;  // TMEM lanes 32 * quarter .. + 31 belong to this warp
     const int row = quarter * 32 + lane;
     const int n = n0 + row;
@@ -277,19 +290,37 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       if (members > 1) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) partial[(c0 + i) * kBlockRows + row] = v[i];
+      } else if (p.fold.x != nullptr) {
+        // Into the residual stream; partial sums of squares per (block, quarter of its rows).
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int m = c0 + i;
+          float sq = 0.f;
+          if (m < p.M && n < p.N) {
+            const int64_t at = static_cast<int64_t>(m) * p.N + n;
+            const float now = p.fold.x[at] + v[i];
+            p.fold.x[at] = now;
+            p.fold.xn[at] = __float2bfloat16_rn(now * p.fold.next_weight[n]);
+            sq = now * now;
+          }
+          sq = warp_sum(sq);
+          if (lane == 0 && m < kFoldTokens)
+            p.fold.ss_out[(static_cast<int64_t>(blockIdx.x) * 4 + quarter) * kFoldTokens + m] = sq;
+        }
       } else if (p.epilogue == EPI_SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float up = __shfl_down_sync(0xffffffffu, v[i], 1);
           const int m = c0 + i;
+          const float gate = scaled && m < p.M ? v[i] * rstd_s[m] : v[i];
+          const float up = __shfl_down_sync(0xffffffffu, gate, 1);
           if ((lane & 1) == 0 && m < p.M && n < p.N)
             static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
-                __float2bfloat16_rn(v[i] / (1.f + expf(-v[i])) * up);
+                __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
         }
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          if (c0 + i < p.M && n < p.N) write_output(p, c0 + i, n, v[i]);
+          if (c0 + i < p.M && n < p.N) write_output(p, c0 + i, n, scaled ? v[i] * rstd_s[c0 + i] : v[i]);
       }
     }
   }
@@ -325,6 +356,10 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
               up += ups[rank];
             }
           }
+          if (scaled) {
+            gate *= rstd_s[m];
+            up *= rstd_s[m];
+          }
           const int n = n0 + r;
           if (n < p.N)
             static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
@@ -341,7 +376,30 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 #pragma unroll
           for (int rank = 0; rank < kMaxMembers; ++rank)
             if (rank < members) sum += values[rank];
-          if (n0 + r < p.N) write_output(p, m, n0 + r, sum);
+          if (scaled) sum *= rstd_s[m];
+          const int n = n0 + r;
+          if (p.fold.x != nullptr) {
+            float sq = 0.f;
+            if (n < p.N) {
+              const int64_t at = static_cast<int64_t>(m) * p.N + n;
+              const float now = p.fold.x[at] + sum;
+              p.fold.x[at] = now;
+              p.fold.xn[at] = __float2bfloat16_rn(now * p.fold.next_weight[n]);
+              sq = now * now;
+            }
+            squares[m * kBlockRows + (r - r_begin)] = sq;
+          } else if (n < p.N) {
+            write_output(p, m, n, sum);
+          }
+        }
+        if (p.fold.x != nullptr) {
+          // This member's partial sums of squares, one per token, added in row order.
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (tid < p.M && tid < kFoldTokens) {
+            float total = 0.f;
+            for (int r = 0; r < rows; ++r) total += squares[tid * kBlockRows + r];
+            p.fold.ss_out[(static_cast<int64_t>(blockIdx.x) * members + blockIdx.y) * kFoldTokens + tid] = total;
+          }
         }
       }
     }
@@ -549,8 +607,45 @@ B200_API void b200_stream_gemm_plan_override(int stages, int target, int members
   g_plan_override.members = members;
 }
 
+static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
+                           const void* next_weights, int64_t next_bytes, const NormFold& fold, cudaStream_t stream);
+
 B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
                               const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
+  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, next_weights, next_bytes, NormFold{}, stream);
+}
+
+// With a folded norm behind it (NormFold in common.cuh): how many rows of partial sums of squares a
+// launch with the residual epilogue writes: one per cluster member, or per quarter of a block
+// that shares its rows with nobody.
+B200_API int b200_stream_gemm_fold_parts(int M, int N, int K) {
+  const StreamPlan plan = plan_stream(N, K, (M + 15) / 16 * 16);
+  return plan.members > 1 ? plan.blocks * plan.members : plan.blocks * 4;
+}
+
+// The same product around a folded RMSNorm; the arguments are those of b200_skinny_gemm_fold.
+B200_API int b200_stream_gemm_fold(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
+                                   const float* ss_in, int ss_parts, int width, float eps, float* x,
+                                   const float* next_weight, void* xn, float* ss_out, cudaStream_t stream) {
+  NormFold fold{};
+  fold.ss_in = ss_in;
+  fold.ss_parts = ss_parts;
+  fold.width = width;
+  fold.eps = eps;
+  fold.x = x;
+  fold.next_weight = next_weight;
+  fold.xn = static_cast<__nv_bfloat16*>(xn);
+  fold.ss_out = ss_out;
+  B200_REQUIRE(M <= kFoldTokens, "stream_gemm_fold: at most %d tokens", kFoldTokens);
+  B200_REQUIRE(ss_in == nullptr || (ss_parts > 0 && width > 0), "stream_gemm_fold: partial sums without their count");
+  B200_REQUIRE(x == nullptr || (next_weight != nullptr && xn != nullptr && ss_out != nullptr && epilogue == EPI_BF16),
+               "stream_gemm_fold: the residual epilogue needs the next norm's scale, xn and ss_out");
+  B200_REQUIRE(x != nullptr || Y != nullptr, "stream_gemm_fold: no output");
+  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, nullptr, 0, fold, stream);
+}
+
+static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
+                           const void* next_weights, int64_t next_bytes, const NormFold& fold, cudaStream_t stream) {
   B200_REQUIRE(b200_stream_gemm_supported(M, N, K, epilogue), "stream_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -567,6 +662,7 @@ B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int 
   p.tmem_cols = 32;
   while (p.tmem_cols < p.tokens_pad) p.tmem_cols *= 2;
   p.epilogue = epilogue;
+  p.fold = fold;
   const StreamPlan plan = plan_stream(N, K, p.tokens_pad);
   p.stages = plan.stages;
   CUtensorMap w_map, x_map;

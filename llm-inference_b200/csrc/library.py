@@ -61,6 +61,10 @@ _SIGNATURES: dict[str, list] = {
     "b200_flash_prefill_tcgen05": [c_void_p] * 8 + [c_int] * 11 + [c_float, c_void_p, c_void_p],
     "b200_skinny_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p],
     "b200_stream_gemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_void_p],
+    "b200_skinny_gemm_fold": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int,
+                              c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "b200_stream_gemm_fold": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                              c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_argmax_rows": [c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "b200_sample_rows": [c_void_p, c_int, c_int, c_int64] + [c_void_p] * 7 + [c_void_p, c_int64, c_void_p],
 }
@@ -87,6 +91,10 @@ class KernelLibrary:
         self.lib.b200_stream_gemm_plan_override.argtypes = [c_int] * 3
         self.lib.b200_stream_gemm_plan_override.restype = None
         self.lib.b200_sm_count.restype = c_int
+        self.lib.b200_skinny_gemm_fold_parts.argtypes = [c_int, c_int]
+        self.lib.b200_skinny_gemm_fold_parts.restype = c_int
+        self.lib.b200_stream_gemm_fold_parts.argtypes = [c_int, c_int, c_int]
+        self.lib.b200_stream_gemm_fold_parts.restype = c_int
         self._functions = {}
         self.calls = 0  # kernel launches issued through this library
         for name, argtypes in _SIGNATURES.items():

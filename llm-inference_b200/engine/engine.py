@@ -101,6 +101,7 @@ class Engine:
         run_ahead: bool = True,
         kernels: str = "tuned",
         decode_kernel: str = "chain",
+        fold_norms: bool = False,
         nvtx: bool = False,
         step_timing: bool = False,
         model: Model | None = None,
@@ -158,6 +159,9 @@ class Engine:
                 # requests as one resident kernel where the model allows it (slower; kept as an option).
                 "decode_kernel": "chain" if kernels == "plain" else decode_kernel,
                 "step_timing": bool(step_timing),
+                # Norms folded into the products around them in short steps (parts/ops.py::fold_enabled):
+                # fewer launches, measured no faster; an option.
+                "fold_norms": bool(fold_norms) and kernels != "plain",
                 **({"attention": "plain", "gemm": "library"} if kernels == "plain" else {}),
             },
         )

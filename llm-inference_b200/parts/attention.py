@@ -74,7 +74,10 @@ class GroupedQueryAttention(Part):
         total = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
         return total + (self.b_qkv.numel() * 4 if self.b_qkv is not None else 0)
 
-    def forward(self, ctx: StepContext, cache: CacheView, h: torch.Tensor) -> torch.Tensor:
+    takes_folded = True  # `h` may be ops.FoldedRows: the q/k/v product applies the norm's 1 / rms
+    takes_sink = True  # with a sink the output product adds into the residual stream itself
+
+    def forward(self, ctx: StepContext, cache: CacheView, h, sink: ops.ResidualSink | None = None):
         t = ctx.num_tokens
         width = (self.q_heads + 2 * self.kv_heads) * self.head_dim
         qkv = ops.linear(ctx, h, self.w_qkv, ctx.buffer("qkv", (t, width)))
@@ -84,6 +87,10 @@ class GroupedQueryAttention(Part):
         self.position.apply(ctx, cache, qkv, self.b_qkv, q, self.q_heads, self.kv_heads, self.head_dim)
         attn = ctx.buffer("attn", (t, self.q_heads * self.head_dim))
         self.attend(ctx, cache, q, attn)
+        if sink is not None:
+            folded = ops.linear_into_residual(ctx, attn, self.w_o, sink)
+            if folded is not None:
+                return folded
         return ops.linear(ctx, attn, self.w_o, ctx.buffer("branch", (t, self.hidden_size)))
 
     def attend(self, ctx: StepContext, cache: CacheView, q: torch.Tensor, out: torch.Tensor) -> None:

@@ -37,12 +37,19 @@ class SwiGLU(Part):
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+    takes_folded = True  # `h` may be ops.FoldedRows: the gate/up product applies the norm's 1 / rms
+    takes_sink = True  # with a sink the down product adds into the residual stream itself
+
+    def forward(self, ctx: StepContext, h, sink: ops.ResidualSink | None = None):
         t, i = ctx.num_tokens, self.intermediate_size
         act = ctx.buffer("act", (t, i))
         if not ops.linear_swiglu(ctx, h, self.w_gate_up, act):
             gate_up = ops.linear(ctx, h, self.w_gate_up, ctx.buffer("gate_up", (t, 2 * i)))
             ops.silu_mul(ctx, gate_up, act)
+        if sink is not None:
+            folded = ops.linear_into_residual(ctx, act, self.w_down, sink)
+            if folded is not None:
+                return folded
         return ops.linear(ctx, act, self.w_down, ctx.buffer("branch", (t, self.hidden_size)))
 
 

@@ -148,13 +148,22 @@ class Model:
                 return resident.run(ctx, cache_views)
         x = self.embedding.forward(ctx)
         delta = None
-        for call in self.schedule:
+        for index, call in enumerate(self.schedule):
             block = self.blocks[call.layer]
             view: CacheView | None = cache_views(call) if block.cache_spec() is not None else None
             with mark(f"layer {call.layer}"):
-                delta = block.forward(ctx, view, x, delta)
+                if getattr(block, "takes_next_norm", False):
+                    # The norm that reads this block's output: a block that adds its last branch
+                    # into the stream by itself folds that norm's scale into what it hands on.
+                    following = self.schedule[index + 1].layer if index + 1 < len(self.schedule) else None
+                    next_norm = getattr(self.blocks[following], "mixer_norm", None) if following is not None else self.final_norm
+                    delta = block.forward(ctx, view, x, delta, next_norm=next_norm)
+                else:
+                    delta = block.forward(ctx, view, x, delta)
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.head.vocab_size), dtype=torch.float32, device=ctx.device)
         with mark("head"):
+            if not isinstance(delta, torch.Tensor) and delta is not None and not getattr(self.final_norm, "foldable", False):
+                delta = None  # the stream is current; this norm knows nothing of the folded form
             h = self.final_norm.forward(ctx, x, delta, rows=ctx.logit_rows, out_name="normed_rows")
             return self.head.forward(ctx, h)

@@ -39,6 +39,7 @@ def make_ctx(lib, token_ids=None, positions=None, token_seq=None, starts=None, r
     ctx = SimpleNamespace(
         lib=lib,
         device=dev,
+        dtype=torch.bfloat16,
         num_tokens=n,
         token_ids=as_dev(token_ids),
         positions=as_dev(positions),
@@ -234,6 +235,60 @@ def gather_cache(arena, table, length, page_size):
     for pos in range(length):
         rows.append(arena[int(table[pos // page_size]), :, pos % page_size, :])
     return torch.stack(rows)
+
+
+@pytest.mark.parametrize("kernel", ["skinny", "tcgen05"])
+@pytest.mark.parametrize("m,hidden,inner,wide", [(8, 1536, 1536, 4096), (3, 264, 520, 1000), (16, 3584, 18944, 4608), (1, 1536, 8960, 2048)])
+def test_norm_folded_into_the_products_around_it(lib, kernel, m, hidden, inner, wide):
+    """A product that adds into the residual stream and hands on the stream times the next norm's
+    scale with partial sums of squares, then products that take that form and apply 1 / rms to
+    their outputs (plain and SwiGLU): against x + a W^T and RMSNorm in float64."""
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(m * 31 + hidden)
+    eps = 1e-5
+    stream = (torch.randn(m, hidden, device="cuda") * 2).contiguous()
+    a = torch.randn(m, inner, device="cuda").to(torch.bfloat16)
+    w_in = (torch.randn(hidden, inner, device="cuda") / math.sqrt(inner)).to(torch.bfloat16)
+    scale = 1 + 0.2 * torch.randn(hidden, device="cuda")
+    w_out = (torch.randn(wide, hidden, device="cuda") / math.sqrt(hidden)).to(torch.bfloat16)
+    ctx = make_ctx(lib, positions=[0] * m)
+    ctx.options.update(gemm=kernel, fold_norms=True)
+    norm = SimpleNamespace(weight=scale, eps=eps, foldable=True)
+    x = stream.clone()
+    folded = ops.linear_into_residual(ctx, a, w_in, ops.ResidualSink(x, norm))
+    assert folded is not None and folded.xn.shape == (m, hidden) and folded.ss.shape == (folded.parts, 16)
+    want_x = stream.double() + a.double() @ w_in.double().T
+    torch.testing.assert_close(x.double(), want_x, atol=2e-3, rtol=2e-3)
+    torch.testing.assert_close(folded.xn.double(), x.double() * scale.double(), atol=3e-2, rtol=1e-2)
+    sums = folded.ss[:, :m].double().sum(0)
+    torch.testing.assert_close(sums, (x.double() ** 2).sum(1), atol=1e-2, rtol=1e-5)
+    normed = x.double() * torch.rsqrt((x.double() ** 2).mean(1, keepdim=True) + eps) * scale.double()
+    # What the separate norm kernel and the plain product give is the yardstick for bfloat16 here.
+    h = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
+    ops.rmsnorm(ctx, x, None, scale, eps, h)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        out = torch.full((m, wide), float("nan"), device="cuda", dtype=out_dtype)
+        ops.linear(ctx, folded, w_out, out)
+        want = normed @ w_out.double().T
+        chain = torch.empty_like(out)
+        ops.linear(ctx, h, w_out, chain)
+        error, floor = (out.double() - want).abs(), (chain.double() - want).abs()
+        assert error.max() <= 1.5 * floor.max() + 1e-3 and error.mean() <= 1.2 * floor.mean() + 1e-4, (error.max(), floor.max())
+    act = torch.full((m, wide // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+    assert ops.linear_swiglu(ctx, folded, w_out, act)
+    y = normed @ w_out.double().T
+    gate, up = y[:, 0::2], y[:, 1::2]
+    chain = torch.empty_like(act)
+    assert ops.linear_swiglu(ctx, h, w_out, chain)
+    want = gate / (1 + torch.exp(-gate)) * up
+    error, floor = (act.double() - want).abs(), (chain.double() - want).abs()
+    assert error.max() <= 1.5 * floor.max() + 1e-3 and error.mean() <= 1.2 * floor.mean() + 1e-4, (error.max(), floor.max())
+    # The same launches again give the same bits (partial sums are added in a fixed order).
+    first_sums = folded.ss[:, :m].clone()
+    x2 = stream.clone()
+    again = ops.linear_into_residual(ctx, a, w_in, ops.ResidualSink(x2, norm))
+    assert torch.equal(x2, x) and torch.equal(again.ss[:, :m], first_sums)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

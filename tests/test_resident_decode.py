@@ -38,7 +38,7 @@ def setting():
     return model, sequences, expected
 
 
-def decode_logits(model, sequences, decode_kernel: str, cuda_graphs: bool):
+def decode_logits(model, sequences, decode_kernel: str, cuda_graphs: bool, fold_norms: bool = False):
     import torch
 
     from llm_inference_b200.engine.engine import Engine
@@ -47,6 +47,7 @@ def decode_logits(model, sequences, decode_kernel: str, cuda_graphs: bool):
     engine = Engine(
         model=model, max_num_sequences=16, max_model_length=1024, kv_cache_bytes=64 << 20, prefill_chunk_size=512,
         prefill_burst_size=512, max_batch_tokens=600, dtype="bfloat16", cuda_graphs=cuda_graphs, decode_kernel=decode_kernel,
+        fold_norms=fold_norms,
     )
     runner = engine.runner
     assert (runner.options["resident"] is not None) == (decode_kernel == "resident")
@@ -98,6 +99,29 @@ def test_resident_decode_steps_match_plain_and_the_chain(setting, live, graphs):
     print(f"live={live}: mean error of the resident kernel over the chain's, per row: mean {np.mean(ratios):.3f}, "
           f"min {np.min(ratios):.3f}, max {np.max(ratios):.3f}")
     assert np.mean(ratios) <= 1.05, ratios  # measured: 0.90 to 0.94
+
+
+@pytest.mark.parametrize("live", [1, 5, 16])
+def test_norms_folded_into_the_products_match_plain_and_the_chain(setting, live):
+    """The option that folds every RMSNorm of a short step into the products around it (the
+    product before adds into the residual stream itself, the product after applies 1 / rms):
+    fewer launches, the same logits to rounding."""
+    model, sequences, expected = setting
+    sequences, expected = sequences[:live], expected[:live]
+    got, launches = decode_logits(model, sequences, "chain", False, fold_norms=True)
+    chain, chain_launches = decode_logits(model, sequences, "chain", False)
+    layers = SHAPE["num_hidden_layers"]
+    assert launches[-1] == chain_launches[-1] - (2 * layers - 1), (launches, chain_launches)  # all norms but the first
+    ratios = []
+    for step in range(DECODED):
+        for i in range(live):
+            want = expected[i][step]
+            error, floor = np.abs(got[step, i] - want), np.abs(chain[step, i] - want)
+            spread = float(want.std())
+            assert error.mean() <= 2.0 * floor.mean() + 0.002 * spread and error.max() <= 2.0 * floor.max() + 0.01 * spread, (
+                live, step, i, error.max() / spread, floor.max() / spread)
+            ratios.append(error.mean() / floor.mean())
+    assert np.mean(ratios) <= 1.1, ratios
 
 
 def test_generation_through_the_engine_uses_the_resident_kernel(setting):
