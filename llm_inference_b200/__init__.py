@@ -8,7 +8,7 @@ from pathlib import Path as _Path
 
 __path__.append(str(_Path(__file__).resolve().parent.parent / "llm-inference_b200"))
 
-from .api import (  # noqa: E402
+from .engine.engine import (  # noqa: E402
     SamplingParams,
     SequenceState,
     TokenEvent,
