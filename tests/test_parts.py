@@ -339,7 +339,8 @@ def test_graph_safe_mixer_with_state_is_replayed_but_never_run_ahead(tmp_path):
 
 
 def register_routed_toy():
-    """A second toy architecture, defined here only: the stock attention mixer with two other
+    """A second toy architecture, defined here only: a norm of its own (mean-subtracting, with a
+    bias) in one layer and before the head, the stock attention mixer with two other
     position encodings (rotary angles of position / 4, as position interpolation does, and in
     the last layer learned per-position offsets, which have no frequency table at all), a routed
     feed-forward (two experts, the better one per token by a 32-bit router) in the odd layers and
@@ -394,6 +395,37 @@ def register_routed_toy():
                 cache.keys[page, :, row] = k.to(cache.keys.dtype)
                 cache.values[page, :, row] = v.to(cache.values.dtype)
             return q_out
+
+    class CenteredNorm(Part):
+        """A norm the framework has never seen: mean-subtracting, with a bias,
+        ``y = (v - mean v) / sqrt(var v + eps) * w + b`` for ``v = x + delta``. What the block asks of a
+        norm is all it provides: add the pending branch output into the 32-bit stream, return the
+        normalised rows in the compute dtype; only the given rows, stream untouched, when asked."""
+
+        graph_safe = False
+
+        def __init__(self, *, name: str, hidden_size: int, eps: float) -> None:
+            self.name, self.hidden_size, self.eps = name, hidden_size, float(eps)
+
+        def tensor_specs(self):
+            return [TensorSpec(self.name + ".weight", (self.hidden_size,), init="one_plus_normal"),
+                    TensorSpec(self.name + ".bias", (self.hidden_size,))]
+
+        def load(self, tensors, dtype, device):
+            self.weight = tensors[self.name + ".weight"].to(device=device, dtype=torch.float32)
+            self.bias = tensors[self.name + ".bias"].to(device=device, dtype=torch.float32)
+
+        def forward(self, ctx, x, delta, rows=None, out_name="normed"):
+            if rows is None:
+                if delta is not None:
+                    x += delta.float()
+                v = x
+            else:
+                picked = rows.long()
+                v = x[picked] if delta is None else x[picked] + delta[picked].float()
+            centred = v - v.mean(-1, keepdim=True)
+            y = centred * torch.rsqrt(centred.square().mean(-1, keepdim=True) + self.eps) * self.weight + self.bias
+            return y.to(ctx.dtype)
 
     class TwoExperts(Part):
         """``out = p * expert_e(h)`` with ``e = argmax(router(h))`` and ``p`` its softmax
@@ -459,6 +491,9 @@ def register_routed_toy():
         def norm(name):
             return PartSpec("rmsnorm", dict(name=name, hidden_size=config.hidden_size, eps=config.eps))
 
+        def centered(name):
+            return PartSpec("centered_norm", dict(name=name, hidden_size=config.hidden_size, eps=config.eps))
+
         def position(i):
             # The last layer encodes positions by learned offsets, the others by squashed rotation.
             if i == config.num_hidden_layers - 1:
@@ -475,7 +510,9 @@ def register_routed_toy():
                 mixer=PartSpec("gqa_attention", dict(
                     prefix=f"layers.{i}.attn.", hidden_size=config.hidden_size, q_heads=config.heads, kv_heads=config.kv_heads,
                     head_dim=config.head_dim, qkv_bias=False, position=position(i))),
-                feed_forward=feed_forward(i), mixer_norm=norm(f"layers.{i}.norm1"), feed_forward_norm=norm(f"layers.{i}.norm2")))
+                feed_forward=feed_forward(i), mixer_norm=norm(f"layers.{i}.norm1"),
+                # Layer 1 normalises its feed-forward input with the toy norm, as the model does its last rows.
+                feed_forward_norm=(centered if i == 1 else norm)(f"layers.{i}.norm2")))
             for i in range(config.num_hidden_layers)
         ]
         # Layer 0 runs twice, the second time with a cache of its own.
@@ -483,14 +520,20 @@ def register_routed_toy():
         return ModelRecipe(
             config=config,
             embedding=PartSpec("token_embedding", dict(name="embed", vocab_size=config.vocab_size, hidden_size=config.hidden_size)),
-            layers=layers, final_norm=norm("norm"), schedule=order,
+            layers=layers, final_norm=centered("norm"), schedule=order,
             head=PartSpec("linear_head", dict(name="head", vocab_size=config.vocab_size, hidden_size=config.hidden_size)))
 
+    register_part("norm", "centered_norm", CenteredNorm, replace=True)
     register_part("position", "squashed_rotary", SquashedRotary, replace=True)
     register_part("position", "learned_offset", LearnedOffset, replace=True)
     register_part("feed_forward", "two_experts", TwoExperts, replace=True)
     register_architecture("ToyRoutedForCausalLM", RoutedConfig.from_json_dict, recipe, replace=True)
     return RoutedConfig
+
+
+def centered_plain(v, weight, bias, eps):
+    centred = v - v.mean(-1, keepdims=True)
+    return centred / np.sqrt((centred * centred).mean(-1, keepdims=True) + eps) * weight + bias
 
 
 def routed_plain(config, weights, tokens):
@@ -509,7 +552,10 @@ def routed_plain(config, weights, tokens):
         else:
             q, k = plain.rope(q, positions, config["theta"]), plain.rope(k, positions, config["theta"])
         x = x + plain.linear(plain.attention(q, k, v, d**-0.5), weights[p + "attn.o_proj.weight"])
-        h = plain.rms_norm(x, weights[p + "norm2.weight"], config["eps"])
+        if i == 1:
+            h = centered_plain(x, weights[p + "norm2.weight"], weights[p + "norm2.bias"], config["eps"])
+        else:
+            h = plain.rms_norm(x, weights[p + "norm2.weight"], config["eps"])
         if i % 2:
             probs = plain.softmax(h @ weights[p + "mlp.router.weight"].T)
             choice = probs.argmax(-1)
@@ -520,7 +566,7 @@ def routed_plain(config, weights, tokens):
             x = x + out
         else:
             x = x + plain.swiglu(h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"])
-    return plain.linear(plain.rms_norm(x, weights["norm.weight"], config["eps"]), weights["head.weight"])
+    return plain.linear(centered_plain(x, weights["norm.weight"], weights["norm.bias"], config["eps"]), weights["head.weight"])
 
 
 def test_toy_position_encoding_and_routed_feed_forward_without_touching_the_framework(tmp_path):
