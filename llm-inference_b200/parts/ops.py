@@ -49,10 +49,11 @@ class ResidualSink:
 def fold_enabled(ctx: StepContext) -> bool:
     """With ``options["fold_norms"]`` norms are folded into the products around them in bfloat16
     steps of up to 16 tokens, where the engine's own weight-streaming products run. Off by
-    default: measured on a B200 (Qwen2.5-1.5B sizes, 8 requests of 2,048 keys) the step has 200
-    launches instead of 255 and takes 1.295 ms instead of 1.229 ms; even with the folded
-    products' extra work left out it takes 1.240 ms, because the norm kernels were already hidden
-    behind the products that follow them (which fetch their weights while the norm runs)."""
+    default: measured on one B200 in alternation (Qwen2.5-1.5B sizes, 8 requests of 2,048 keys)
+    the step has 200 launches instead of 255 and takes 1.293 ms instead of 1.284 ms; with the
+    folded products' extra work (partial sums of squares, 1 / rms) left out altogether it takes
+    1.263 ms, so 1.6 % is all there is to gain: the norm kernels are hidden behind the products
+    that follow them, which fetch their weights while the norm runs."""
     return (
         ctx.dtype == torch.bfloat16 and 0 < ctx.num_tokens <= 16 and bool(ctx.options.get("fold_norms", False))
         and ctx.options.get("gemm", "auto") != "library"
