@@ -36,10 +36,11 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
 
 
-def ptr(tensor: torch.Tensor | None) -> c_void_p:
-    if tensor is None:
-        return c_void_p(0)
-    return c_void_p(tensor.data_ptr())
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """A tensor's device address as ctypes takes it for a declared ``c_void_p`` parameter: a plain
+    int (None for a null pointer). No ctypes object is built per argument: a step makes some two
+    thousand of these calls."""
+    return None if tensor is None else tensor.data_ptr()
 
 
 def stream_handle() -> c_void_p:

@@ -150,4 +150,4 @@ class StepContext:
     def stream(self):
         """The current CUDA stream's handle (looked up at every launch: it changes while a
         graph is being captured)."""
-        return c_void_p(_raw_stream(self.device))
+        return _raw_stream(self.device)

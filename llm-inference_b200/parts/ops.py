@@ -527,10 +527,8 @@ def paged_prefill_attention_tcgen05(
     return out
 
 
-def _offset(tensor: torch.Tensor, nbytes: int):
-    from ctypes import c_void_p
-
-    return c_void_p(tensor.data_ptr() + nbytes)
+def _offset(tensor: torch.Tensor, nbytes: int) -> int:
+    return tensor.data_ptr() + nbytes
 
 
 def argmax_rows(lib, logits: torch.Tensor, out: torch.Tensor, row_index: torch.Tensor | None, rows: int, stream) -> None:
