@@ -152,7 +152,7 @@ def reference_arm(args) -> int:
     if not (REFERENCE_DIR / "instinct").is_dir():
         return unavailable(
             "the reference is not installed under baseline/_ref (offline install: pip --no-deps from a writable copy, "
-            "with the CMake target CUDA::nvToolsExt supplied by baseline/nvtx_shim; see DESIGN.md)"
+            "with the CMake target CUDA::nvToolsExt supplied by baseline/nvtx_shim/project_include.cmake)"
         )
     sys.path.insert(0, str(REFERENCE_DIR))
     try:
