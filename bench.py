@@ -396,6 +396,8 @@ def main() -> int:
         "value": PROMPT / (prefill_ms / 1e3), "tokens": PROMPT, "ms": prefill_ms,
         "frac": prefill_flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12),
     }
+    if peak.get("bf16_tflops_sustained"):  # the library's rate in a seconds-long loop under the power cap
+        prefill["frac_of_sustained"] = prefill_flops / (prefill_ms / 1e3) / (peak["bf16_tflops_sustained"] * 1e12)
 
     # --- decode, timed on the device -------------------------------------------------------------
     def decode_point(batch: int, k: int, w: int) -> dict:
@@ -450,6 +452,19 @@ def main() -> int:
     if not args.no_points:
         for batch in (1, 64):
             points[f"decode_b{batch}"] = decode_point(batch, max(16, steps // 2), warmup)["tokens_per_s"]
+        # The same steps with the slow, simple kernels the tuned ones are checked against (the plain
+        # attention kernel, the library's matrix products everywhere): a stated baseline of this
+        # repository's own, since the reference's CUDA engine does not run (see --impl reference).
+        saved = {name: runner.options.get(name) for name in ("attention", "gemm")}
+        runner.options.update(attention="plain", gemm="library")
+        runner._graphs.clear()
+        points[f"decode_b{args.batch}_plain_kernels"] = decode_point(args.batch, max(16, steps // 2), warmup)["tokens_per_s"]
+        for name, value in saved.items():
+            if value is None:
+                runner.options.pop(name, None)
+            else:
+                runner.options[name] = value
+        runner._graphs.clear()
 
     # --- the same through the public entry point: host tokens in and out ------------------------
     prompts = [[int(t) for t in rng.integers(0, vocab, prompt_len)] for _ in range(args.batch)]
