@@ -237,10 +237,67 @@ def bench_resident(args) -> dict:
             "kernel_us": float(stamps[-1, 2] - stamps[0, 0]), "phases": summary}
 
 
+def bench_timeline(args) -> dict:
+    """One layer of a replayed decode step on the timeline: for every kernel of the step's second
+    layer, when its first block started, when it ended and how long after its predecessor's end
+    (Kineto timestamps through torch.profiler; no kernel is replayed or serialised)."""
+    import numpy as np
+    from torch.profiler import ProfilerActivity, profile
+
+    from .. import models  # noqa: F401
+    from ..config import parse_config
+    from ..engine.engine import Engine
+    from ..engine.loading import random_model
+    from ..engine.runner import StepEntry
+    from .presets import PRESETS
+
+    _, config = parse_config(dict(PRESETS[args.shape]))
+    model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    kv_bytes = 2 * config.num_hidden_layers * config.num_key_value_heads * config.head_dim * 2 * args.batch * (args.context + 256)
+    engine = Engine(model=model, max_num_sequences=max(16, args.batch), max_model_length=2 * args.context,
+                    kv_cache_bytes=kv_bytes + (1 << 30), prefill_chunk_size=2048, prefill_burst_size=2048,
+                    max_batch_tokens=2048 + max(16, args.batch))
+    runner = engine.runner
+    rng = np.random.default_rng(0)
+    ids = list(range(1, args.batch + 1))
+    for rid in ids:
+        engine.cache.open(rid)
+        for begin in range(0, args.context, 2048):
+            runner.step([StepEntry(rid, [int(t) for t in rng.integers(0, config.vocab_size, min(2048, args.context - begin))], ())])
+    step = lambda: runner.step([StepEntry(rid, (int(rng.integers(0, config.vocab_size)),), (0,)) for rid in ids])
+    for _ in range(6):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+    firsts = [i for i, e in enumerate(events) if "embedding" in e.name]
+    if len(firsts) < 3:
+        raise SystemExit("the profiler did not see three steps")
+    per_step = firsts[2] - firsts[1]
+    # The second layer of the middle step: from its first norm to the next layer's first norm
+    # (two norm kernels per layer in the stock arrangement).
+    norms = [i for i in range(firsts[1], firsts[2]) if "rmsnorm" in events[i].name]
+    if len(norms) < 5:
+        raise SystemExit("the step does not show two norm kernels per layer")
+    start, per_layer = norms[2], norms[4] - norms[2]
+    origin = events[firsts[1]].time_range.start
+    rows, previous_end = [], events[start - 1].time_range.end
+    for e in events[start : start + per_layer]:
+        rows.append({"kernel": e.name[:60], "start_us": round(e.time_range.start - origin, 1),
+                     "end_us": round(e.time_range.end - origin, 1), "after_us": round(e.time_range.end - previous_end, 1)})
+        previous_end = e.time_range.end
+    engine.close()
+    return {"kernel": "decode step timeline", "shape": args.shape, "batch": args.batch, "context": args.context,
+            "kernels_per_step": per_step, "layer_us": round(sum(r["after_us"] for r in rows), 1), "layer": rows}
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident"])
-    parser.add_argument("--shape", default="qwen2.5-1.5b", help="resident: a named model shape")
+    parser.add_argument("kernel", choices=["gemm", "decode_attention", "prefill_attention", "resident", "timeline"])
+    parser.add_argument("--shape", default="qwen2.5-1.5b", help="resident, timeline: a named model shape")
     parser.add_argument("--m", type=int, default=8)
     parser.add_argument("--n", type=int, default=17920)
     parser.add_argument("--k", type=int, default=1536)
@@ -273,6 +330,8 @@ def main(argv=None) -> int:
         result = bench_gemm(args)
     elif args.kernel == "resident":
         result = bench_resident(args)
+    elif args.kernel == "timeline":
+        result = bench_timeline(args)
     else:
         result = bench_attention(args, args.kernel == "decode_attention")
     print(json.dumps(result))
