@@ -91,6 +91,51 @@ def time_back_to_back(fns, launches: int) -> float:
     return start.elapsed_time(end) * 1e3 / launches
 
 
+TRACE_POINTS = ("resident", "predecessor done", "first stage landed", "last stage landed", "accumulator complete",
+                "partial tiles met", "slice stored", "leaving")
+
+
+def trace_back_to_back(lib, fns, launches: int) -> dict:
+    """The tcgen05 product's own timeline (b200_stream_gemm_trace) of ``launches`` launches that run
+    back to back in a CUDA graph: for every point of a block's life, when the first, the median
+    and the last block of a launch passed it, in microseconds after the last block of the launch
+    in front left; averaged over the later half of the launches."""
+    from ..csrc.library import ptr
+
+    for fn in fns:
+        fn()
+    torch.cuda.synchronize()
+    stamps = lib.b200_stream_gemm_trace_stamps()
+    stride = 4096 * stamps
+    buffer = torch.zeros(launches, stride, dtype=torch.int64, device="cuda")
+    lib.b200_stream_gemm_trace(ptr(buffer), launches, stride)
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(graph):
+            for i in range(launches):
+                fns[i % len(fns)]()
+    finally:
+        lib.b200_stream_gemm_trace(None, 0, 0)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    data = buffer.cpu().numpy().reshape(launches, -1, stamps)
+    blocks = int((data[1, :, 0] != 0).sum())
+    data = data[:, :blocks, :].astype(np.float64) / 1e3  # microseconds
+    rows = {name: [] for name in TRACE_POINTS}
+    spans = []
+    for j in range(launches // 2, launches):
+        origin = data[j - 1, :, stamps - 1].max()
+        spans.append(data[j, :, stamps - 1].max() - origin)
+        for i, name in enumerate(TRACE_POINTS):
+            column = data[j, :, i]
+            column = column[column != 0]
+            if column.size:
+                rows[name].append((column.min() - origin, float(np.median(column)) - origin, column.max() - origin))
+    table = {name: [round(float(v), 2) for v in np.mean(np.array(values), axis=0)] for name, values in rows.items() if values}
+    return {"blocks": blocks, "us_per_launch": round(float(np.mean(spans)), 2), "first_median_last_us": table}
+
+
 def bench_gemm(args) -> dict:
     from ..parts import ops
 
@@ -112,6 +157,11 @@ def bench_gemm(args) -> dict:
             fns = [lambda wi=wi: ops.linear_swiglu(ctx, x, wi, out) for wi in weights]
         else:
             fns = [lambda wi=wi: ops.linear(ctx, x, wi, out) for wi in weights]
+        if args.trace:
+            if args.gemm != "tcgen05":
+                raise SystemExit("--trace records the tcgen05 product's own timestamps: give --gemm tcgen05")
+            return {"kernel": "gemm", "m": m, "n": n, "k": k, "swiglu": args.swiglu, "mode": "back-to-back, traced",
+                    **trace_back_to_back(ctx.lib.lib, fns, 4 * copies)}
         us = time_back_to_back(fns, 4 * copies)
         nbytes = w.numel() * 2 + x.numel() * 2 + out.numel() * out.element_size()
         return {"kernel": "gemm", "m": m, "n": n, "k": k, "gemm": args.gemm, "swiglu": args.swiglu, "mode": "back-to-back",
@@ -306,6 +356,8 @@ def main(argv=None) -> int:
     parser.add_argument("--library", action="store_true", help="time the vendor library's product instead")
     parser.add_argument("--gemm", default="auto", choices=["auto", "tcgen05", "skinny", "library"])
     parser.add_argument("--rotate", action="store_true", help="launch back to back over rotating copies of the weights")
+    parser.add_argument("--trace", action="store_true",
+                        help="with --rotate --gemm tcgen05: the blocks' own timestamps instead of the launch time")
     parser.add_argument("--plan", type=int, nargs=3, metavar=("STAGES", "BLOCKS", "CLUSTER"), default=None,
                         help="tcgen05 product: force ring depth, blocks aimed at and cluster width (0 = the planner's choice)")
     parser.add_argument("--batch", type=int, default=8)

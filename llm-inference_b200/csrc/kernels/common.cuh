@@ -78,6 +78,25 @@ __device__ __forceinline__ float load_peer_f32(const float* local, uint32_t rank
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
+__device__ __forceinline__ float4 load_peer_f32x4(const float* local, uint32_t rank) {  // 16-byte aligned
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void store_peer_f32(float* local, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
 
 // RMSNorm folded into the matrix products around it (decode steps of up to 16 tokens).
 //

@@ -66,10 +66,13 @@ __device__ __forceinline__ float block_sum_at(const float* partial, int k_splits
   return sum;
 }
 
-template <int MT>
+// One instantiation per (token tiles, epilogue, folded norm or not): a block runs its epilogue
+// once, from a cold instruction cache, and code it shares with forms it does not take costs it
+// time (measured on the tcgen05 product, gemm_tcgen05.cu).
+template <int MT, int EPI, bool FOLDED>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
-                   void* __restrict__ Y, int M, int N, int K, int row_groups, int epilogue,
+                   void* __restrict__ Y, int M, int N, int K, int row_groups,
                    float* __restrict__ scratch, int* __restrict__ counters, const void* __restrict__ next_weights,
                    long long next_bytes, const NormFold fold) {
   // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
@@ -127,7 +130,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
 #pragma unroll
   for (int i = 0; i < kStages; ++i) fetch_x(c_begin + i, i);
   copy_async_commit();
-  if (fold.ss_in != nullptr) {
+  if (FOLDED && fold.ss_in != nullptr) {
     // The operand is the stream times a norm's scale: each token's 1 / rms, applied to the sums
     // at the end. Two tokens per warp, while the first slabs are on their way.
     for (int m = warp; m < M; m += kSkinnyWarps) {
@@ -195,7 +198,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
   }
 
   const int block_n0 = blockIdx.x * block_rows;
-  const bool scaled = fold.ss_in != nullptr;
+  const bool scaled = FOLDED && fold.ss_in != nullptr;
   auto total = [&](int r, int m) -> float {
     float sum = 0.f;
     if (sums == nullptr) {
@@ -206,10 +209,10 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     }
     return scaled ? sum * rstd_s[m] : sum;
   };
-  if (fold.x != nullptr) {
+  if (FOLDED && fold.x != nullptr) {
     // The product goes into the residual stream; the stream times the next norm's scale and this
     // block's partial sums of squares go out for the product that follows that norm.
-    __shared__ float squares[kFoldTokens * kSkinnyWarps * 16];  // [m][row of the block]
+    __shared__ float squares[FOLDED ? kFoldTokens * kSkinnyWarps * 16 : 1];  // [m][row of the block]
     for (int item = threadIdx.x; item < M * block_rows; item += kSkinnyThreads) {
       const int m = item / block_rows, r = item - m * block_rows;
       const int n = block_n0 + r;
@@ -231,7 +234,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
     }
     return;
   }
-  if (epilogue == EPI_SWIGLU) {
+  if constexpr (EPI == EPI_SWIGLU) {
     const int pairs = block_rows / 2;
     for (int item = threadIdx.x; item < M * pairs; item += kSkinnyThreads) {
       const int m = item / pairs, j = item - m * pairs;
@@ -247,7 +250,7 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __r
       const int n = block_n0 + r;
       if (n >= N) continue;
       const float sum = total(r, m);
-      if (epilogue == EPI_F32) static_cast<float*>(Y)[static_cast<int64_t>(m) * N + n] = sum;
+      if constexpr (EPI == EPI_F32) static_cast<float*>(Y)[static_cast<int64_t>(m) * N + n] = sum;
       else static_cast<__nv_bfloat16*>(Y)[static_cast<int64_t>(m) * N + n] = __float2bfloat16_rn(sum);
     }
   }
@@ -280,33 +283,61 @@ SkinnyPlan plan_skinny(int N, int K) {
   return plan;
 }
 
-template <int MT>
-int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
-                  const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
-                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false,
-                  const NormFold& fold = NormFold{}) {
+template <int MT, int EPI, bool FOLDED>
+int launch_skinny_as(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
+                     const SkinnyPlan& plan, float* scratch, int* counters, cudaStream_t stream,
+                     const void* next_weights, long long next_bytes, bool ordered, const NormFold& fold) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
   const size_t ring = static_cast<size_t>(kSkinnyWarps) * SkinnyStages<MT>::value * (2 + MT) * 32 * 16;
   const size_t sums = static_cast<size_t>(k_splits) * block_rows * MT * 8 * sizeof(float);
   const size_t smem = ring > sums ? ring : sums;
   // The shared-memory opt-in is a property of the function on one device: set once per device.
-  static size_t configured[kSkinnyMaxDevices] = {};
+  static size_t configured[kSkinnyMaxDevices] = {};  // one array per instantiation
   int device = -1;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kSkinnyMaxDevices)
     return b200_fail("skinny_gemm: cannot tell the current device");
   if (configured[device] < smem) {
-    if (cudaFuncSetAttribute(skinny_gemm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(skinny_gemm_kernel<MT, EPI, FOLDED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return b200_fail("skinny_gemm: cannot size shared memory");
     configured[device] = smem;
   }
   const dim3 grid(plan.blocks, plan.column_blocks);
-  cudaError_t status = launch_kernel_as(ordered, skinny_gemm_kernel<MT>, grid, dim3(kSkinnyThreads), smem, stream, W, X,
-                                        Y, M, N, K, plan.row_groups, epilogue, scratch, counters, next_weights,
+  cudaError_t status = launch_kernel_as(ordered, skinny_gemm_kernel<MT, EPI, FOLDED>, grid, dim3(kSkinnyThreads), smem,
+                                        stream, W, X, Y, M, N, K, plan.row_groups, scratch, counters, next_weights,
                                         next_bytes, fold);
   if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
   return 0;
+}
+
+template <int MT, int EPI>
+int launch_skinny_epilogue(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
+                           const SkinnyPlan& plan, float* scratch, int* counters, cudaStream_t stream,
+                           const void* next_weights, long long next_bytes, bool ordered, const NormFold& fold) {
+  if (fold.ss_in != nullptr || fold.x != nullptr)
+    return launch_skinny_as<MT, EPI, true>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights, next_bytes,
+                                           ordered, fold);
+  return launch_skinny_as<MT, EPI, false>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights, next_bytes,
+                                          ordered, fold);
+}
+
+template <int MT>
+int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
+                  const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
+                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false,
+                  const NormFold& fold = NormFold{}) {
+  switch (epilogue) {
+    case EPI_F32:
+      return launch_skinny_epilogue<MT, EPI_F32>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
+                                                 next_bytes, ordered, fold);
+    case EPI_SWIGLU:
+      return launch_skinny_epilogue<MT, EPI_SWIGLU>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
+                                                    next_bytes, ordered, fold);
+    default:
+      return launch_skinny_epilogue<MT, EPI_BF16>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
+                                                  next_bytes, ordered, fold);
+  }
 }
 
 }  // namespace

@@ -40,6 +40,16 @@ constexpr int kBlockK = 64;      // k per stage: 128 bytes of bf16 = one swizzle
 constexpr int kMmaK = 16;
 constexpr int kMaxMembers = 16;  // blocks of a cluster that share rows of W
 constexpr int kMaxStages = 12;    // the launcher picks the depth from how many blocks share an SM
+constexpr int kPushTokens = 16;  // up to this many (padded) tokens a cluster's partial sums are pushed to their owners
+// Rows of a block that one cluster member finishes: gate/up pairs stay together, and where up to
+// kWideSliceMembers members fetch their slices from each other, four rows to a load, a slice
+// starts on a multiple of four rows.
+constexpr int kWideSliceMembers = 4;
+__host__ __device__ constexpr int slice_rows(int members, int tokens_pad) {
+  const int even = ((kBlockRows + members - 1) / members + 1) & ~1;
+  return tokens_pad > kPushTokens && members <= kWideSliceMembers ? (even + 3) & ~3 : even;
+}
+static_assert(kPushTokens >= kFoldTokens, "a product around a folded norm always takes the push form");
 constexpr int kThreadsT = 192;   // warp 0: TMA, warp 1: MMA, warps 2-5: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
 constexpr int ERRBIT_TIMEOUT = 8;
@@ -138,15 +148,144 @@ struct StreamParams {
   int M, N, K;
   int tokens_pad;  // MMA N: M rounded up to a multiple of 16
   int tmem_cols;   // power of two >= max(32, tokens_pad)
-  int epilogue;
+  long long* trace;  // kTraceStamps timestamps per block when a sweep asked for them, else null
   NormFold fold;   // RMSNorm folded into this product (common.cuh); all null when unused
 };
 
+// The kernel is compiled once per (epilogue, way the cluster adds up, folded norm or not, traced or
+// not): a block runs its epilogue once, from a cold instruction cache, and every form that shares
+// the kernel's code with the others makes each of them slower (the one-for-all kernel had 85 KB
+// of code; with the timestamps compiled in but switched off, 110 KB and 1.2 us more per product
+// inside a decode step of 64 requests).
+enum : int { MODE_SINGLE = 0, MODE_PUSH = 1, MODE_PULL = 2 };
+
+template <int EPI>
 __device__ __forceinline__ void write_output(const StreamParams& p, int m, int n, float v) {
-  if (p.epilogue == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v;
+  if constexpr (EPI == EPI_F32) static_cast<float*>(p.y)[static_cast<int64_t>(m) * p.N + n] = v;
   else static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(v);
 }
 
+// A cluster member's slice of the rows, added up over the members' partial tiles
+// ([tokens_pad][128 rows] in each member's shared memory) and written out; the sums run in member
+// order. Two forms, chosen by the cluster's width from measurements (gate/up of 64 tokens, two
+// members: 18.8 us with one 4-byte load per value and one item per round trip, 14.6 us in the wide
+// form; down of 64 tokens, sixteen members: 10.9 us in the narrow form, 12.1 and 13.7 us with 8-
+// and 16-byte loads).
+//
+// Wide, for up to kWideSliceMembers members: an item is four consecutive rows of one token (two
+// gate/up pairs), fetched from each member with one 16-byte load; the slice starts on a multiple
+// of four rows. A thread takes ITEMS items at a time and asks for all their values before it
+// uses the first: one round trip through the cluster's shared memory per ITEMS items.
+template <int EPI, int RANKS, int ITEMS>
+__device__ __forceinline__ void pull_slices_wide(const StreamParams& p, const float* partial, int members, int tid,
+                                                 int rows, int r_begin, int n0) {
+  const int columns = (rows + 3) / 4;
+  const int total = columns * p.M;
+  constexpr bool swiglu = EPI == EPI_SWIGLU;
+  for (int base = tid; base < total; base += 128 * ITEMS) {
+    float4 part[ITEMS][RANKS];
+#pragma unroll
+    for (int q = 0; q < ITEMS; ++q) {
+      const int item = base + q * 128;
+      const int m = item / columns, r = r_begin + (item - m * columns) * 4;
+#pragma unroll
+      for (int rank = 0; rank < RANKS; ++rank)
+        if (item < total && rank < members) part[q][rank] = load_peer_f32x4(partial + m * kBlockRows + r, rank);
+    }
+#pragma unroll
+    for (int q = 0; q < ITEMS; ++q) {
+      const int item = base + q * 128;
+      if (item >= total) break;
+      const int m = item / columns, r = r_begin + (item - m * columns) * 4;
+      float values[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int rank = 0; rank < RANKS; ++rank) {
+        if (rank < members) {
+          values[0] += part[q][rank].x;
+          values[1] += part[q][rank].y;
+          values[2] += part[q][rank].z;
+          values[3] += part[q][rank].w;
+        }
+      }
+      const int n = n0 + r;
+      const int live = min(4, min(r_begin + rows - r, p.N - n));  // rows of the item inside the slice and the matrix
+      if (swiglu) {
+#pragma unroll
+        for (int i = 0; i < 4; i += 2)
+          if (i + 1 < live)
+            static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + (n + i) / 2] =
+                __float2bfloat16_rn(values[i] / (1.f + expf(-values[i])) * values[i + 1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i < live) write_output<EPI>(p, m, n + i, values[i]);
+      }
+    }
+  }
+}
+
+// Narrow, for wider clusters: an item is one row of one token (a gate/up pair for the SwiGLU
+// epilogue), every member's value asked for with a 4-byte load before the first is used.
+template <int EPI>
+__device__ __forceinline__ void pull_slices_narrow(const StreamParams& p, const float* partial, int members, int tid,
+                                                   int rows, int r_begin, int n0) {
+  if constexpr (EPI == EPI_SWIGLU) {
+    const int pairs = rows / 2;
+    for (int item = tid; item < pairs * p.M; item += 128) {
+      const int m = item / pairs, r = r_begin + 2 * (item - m * pairs);
+      float gates[kMaxMembers], ups[kMaxMembers];
+#pragma unroll
+      for (int rank = 0; rank < kMaxMembers; ++rank) {
+        if (rank < members) {
+          gates[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
+          ups[rank] = load_peer_f32(partial + m * kBlockRows + r + 1, rank);
+        }
+      }
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int rank = 0; rank < kMaxMembers; ++rank) {
+        if (rank < members) {
+          gate += gates[rank];
+          up += ups[rank];
+        }
+      }
+      const int n = n0 + r;
+      if (n < p.N)
+        static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
+            __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
+    }
+  } else {
+    for (int item = tid; item < rows * p.M; item += 128) {
+      const int m = item / rows, r = r_begin + (item - m * rows);
+      float values[kMaxMembers];
+#pragma unroll
+      for (int rank = 0; rank < kMaxMembers; ++rank)
+        if (rank < members) values[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
+      float sum = 0.f;
+#pragma unroll
+      for (int rank = 0; rank < kMaxMembers; ++rank)
+        if (rank < members) sum += values[rank];
+      const int n = n0 + r;
+      if (n < p.N) write_output<EPI>(p, m, n, sum);
+    }
+  }
+}
+
+// Where a block is in its life, for cli/microbench.py's trace: the nanosecond timer at eight
+// points, one writer each. The kernel that records them is an instantiation of its own: even
+// switched off at run time the stamps cost the products 0.2 to 0.8 us each (the branches around
+// them sit in the loops that issue the MMAs and in the epilogue).
+constexpr int kTraceStamps = 8;
+template <bool TRACED>
+__device__ __forceinline__ void stamp(const StreamParams& p, int which) {
+  if constexpr (!TRACED) return;
+  if (p.trace == nullptr) return;
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  p.trace[(static_cast<int64_t>(blockIdx.y) * gridDim.x + blockIdx.x) * kTraceStamps + which] = t;
+}
+
+template <int EPI, int MODE, bool FOLDED, bool TRACED>
 __global__ void __launch_bounds__(kThreadsT)
 stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map,
                    const StreamParams p) {
@@ -162,7 +301,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_base_shared;
   __shared__ float rstd_s[kFoldTokens];
-  __shared__ float squares[kFoldTokens * kBlockRows];  // [m][row of this member's slice]
+  __shared__ float squares[FOLDED ? kFoldTokens * kBlockRows : 1];  // [m][row of this member's slice]
+  constexpr bool clustered = MODE != MODE_SINGLE, push = MODE == MODE_PUSH;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = p.stages;
@@ -176,6 +316,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 
   if (threadIdx.x == 0) {
     let_successor_start();
+    stamp<TRACED>(p, 0);  // the block is resident
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -208,6 +349,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     const int first = min(num_kb, stages);
     wait_for_predecessor();
     let_successor_start();
+    stamp<TRACED>(p, 1);  // the kernel in front is complete
     for (int i = 0; i < first; ++i)
       tma_load_2d(tiles + i * stage_bytes + w_bytes, &x_map, &full_bar[i], (kb_begin + i) * kBlockK, 0);
     for (int i = first; i < num_kb; ++i) {
@@ -243,6 +385,8 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (leader && i == 0) stamp<TRACED>(p, 2);           // the first stage has landed
+      if (leader && i == num_kb - 1) stamp<TRACED>(p, 3);  // the last one has
       const uint64_t stage_units = static_cast<uint64_t>(s) * (stage_bytes >> 4);
 #pragma unroll
       for (int k = 0; k < kBlockK / kMmaK; ++k) {
@@ -257,8 +401,18 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   __syncwarp();
 
   // ---- epilogue: TMEM -> registers -> global, or -> shared memory when the cluster splits K ----
+  // A cluster's members each hold a partial tile; member r finishes rows [r * slice, (r + 1) * slice).
+  // With up to kPushTokens tokens every member writes its values straight into the shared memory
+  // of the row's owner (an inbox behind the ring, which a member that is still streaming does
+  // not touch), the cluster meets once, and each owner adds up what lies in its own memory and
+  // may leave when it is done. With more tokens the inboxes would cost the ring its depth: the
+  // members then put their tiles into their own rings, meet, fetch their slices from each other
+  // with several items' loads in flight at once, and meet again before any of them leaves.
+  const int slice = slice_rows(members, p.tokens_pad);
   float* partial = reinterpret_cast<float*>(tiles);  // [tokens_pad][128 rows]; the stages are idle by then
-  const bool scaled = p.fold.ss_in != nullptr;
+  float* inbox = reinterpret_cast<float*>(tiles + static_cast<size_t>(stages) * stage_bytes);  // [members][M][slice]
+  const bool scaled = FOLDED && p.fold.ss_in != nullptr;
+  const bool residual = FOLDED && p.fold.x != nullptr;  // the product is added into the residual stream
   if (warp >= 2) {
     wait_for_predecessor();
     if (scaled) {
@@ -279,6 +433,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       have = false;
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (threadIdx.x == 64) stamp<TRACED>(p, 4);  // the accumulator is complete
     for (int c0 = 0; c0 < p.tokens_pad; c0 += 16) {
       float v[16];
       if (have) {
@@ -287,10 +442,16 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = 0.f;
       }
-      if (members > 1) {
+      if (push) {
+        const int owner = row / slice;
+        float* mine = inbox + (static_cast<int>(blockIdx.y) * p.M + c0) * slice + (row - owner * slice);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (c0 + i < p.M) store_peer_f32(mine + i * slice, owner, v[i]);
+      } else if (clustered) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) partial[(c0 + i) * kBlockRows + row] = v[i];
-      } else if (p.fold.x != nullptr) {
+      } else if (residual) {
         // Into the residual stream; partial sums of squares per (block, quarter of its rows).
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -307,7 +468,7 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           if (lane == 0 && m < kFoldTokens)
             p.fold.ss_out[(static_cast<int64_t>(blockIdx.x) * 4 + quarter) * kFoldTokens + m] = sq;
         }
-      } else if (p.epilogue == EPI_SWIGLU) {
+      } else if (EPI == EPI_SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int m = c0 + i;
@@ -320,79 +481,63 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       } else {
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          if (c0 + i < p.M && n < p.N) write_output(p, c0 + i, n, scaled ? v[i] * rstd_s[c0 + i] : v[i]);
+          if (c0 + i < p.M && n < p.N) write_output<EPI>(p, c0 + i, n, scaled ? v[i] * rstd_s[c0 + i] : v[i]);
       }
     }
   }
-  if (members > 1) {
+  if (clustered) {
     // Every thread of every member meets here; then each member finishes its slice of the rows.
     cluster_sync_all();
-    int slice = (kBlockRows + members - 1) / members;
-    slice += slice & 1;  // gate/up pairs stay together
+    if (threadIdx.x == 64) stamp<TRACED>(p, 5);  // every member's partial sums are where their owner reads them
     const int r_begin = blockIdx.y * slice, r_end = min(kBlockRows, r_begin + slice);
-    if (warp >= 2) {
+    const int rows = max(0, r_end - r_begin);
+    if (warp >= 2 && push) {
+      // The sums run in member order over this block's own inbox.
       const int tid = threadIdx.x - 64;
-      const int rows = max(0, r_end - r_begin);
-      if (p.epilogue == EPI_SWIGLU) {
+      const int plane = p.M * slice;
+      if (EPI == EPI_SWIGLU) {
         const int pairs = rows / 2;
         for (int item = tid; item < pairs * p.M; item += 128) {
           const int m = item / pairs, j = item - m * pairs;
-          const int r = r_begin + 2 * j;
-          // All members' values are requested before the first is used: one round trip through
-          // the cluster's shared memory, not one per member. The sums run in member order.
-          float gates[kMaxMembers], ups[kMaxMembers];
-#pragma unroll
-          for (int rank = 0; rank < kMaxMembers; ++rank) {
-            if (rank < members) {
-              gates[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
-              ups[rank] = load_peer_f32(partial + m * kBlockRows + r + 1, rank);
-            }
-          }
+          const float* at = inbox + m * slice + 2 * j;
           float gate = 0.f, up = 0.f;
-#pragma unroll
-          for (int rank = 0; rank < kMaxMembers; ++rank) {
-            if (rank < members) {
-              gate += gates[rank];
-              up += ups[rank];
-            }
+          for (int rank = 0; rank < members; ++rank) {
+            const float2 both = *reinterpret_cast<const float2*>(at + rank * plane);
+            gate += both.x;
+            up += both.y;
           }
           if (scaled) {
             gate *= rstd_s[m];
             up *= rstd_s[m];
           }
-          const int n = n0 + r;
+          const int n = n0 + r_begin + 2 * j;
           if (n < p.N)
             static_cast<__nv_bfloat16*>(p.y)[static_cast<int64_t>(m) * (p.N / 2) + n / 2] =
                 __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
         }
       } else {
         for (int item = tid; item < rows * p.M; item += 128) {
-          const int m = item / rows, r = r_begin + (item - m * rows);
-          float values[kMaxMembers];
-#pragma unroll
-          for (int rank = 0; rank < kMaxMembers; ++rank)
-            if (rank < members) values[rank] = load_peer_f32(partial + m * kBlockRows + r, rank);
+          const int m = item / rows, r = item - m * rows;
+          const float* at = inbox + m * slice + r;
           float sum = 0.f;
-#pragma unroll
-          for (int rank = 0; rank < kMaxMembers; ++rank)
-            if (rank < members) sum += values[rank];
+          for (int rank = 0; rank < members; ++rank) sum += at[rank * plane];
           if (scaled) sum *= rstd_s[m];
-          const int n = n0 + r;
-          if (p.fold.x != nullptr) {
+          const int n = n0 + r_begin + r;
+          if (residual) {
             float sq = 0.f;
             if (n < p.N) {
-              const int64_t at = static_cast<int64_t>(m) * p.N + n;
-              const float now = p.fold.x[at] + sum;
-              p.fold.x[at] = now;
-              p.fold.xn[at] = __float2bfloat16_rn(now * p.fold.next_weight[n]);
+              const int64_t to = static_cast<int64_t>(m) * p.N + n;
+              const float now = p.fold.x[to] + sum;
+              p.fold.x[to] = now;
+              p.fold.xn[to] = __float2bfloat16_rn(now * p.fold.next_weight[n]);
               sq = now * now;
             }
-            squares[m * kBlockRows + (r - r_begin)] = sq;
+            squares[m * kBlockRows + r] = sq;
           } else if (n < p.N) {
-            write_output(p, m, n, sum);
+            write_output<EPI>(p, m, n, sum);
           }
         }
-        if (p.fold.x != nullptr) {
+        if (residual) {
           // This member's partial sums of squares, one per token, added in row order.
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (tid < p.M && tid < kFoldTokens) {
@@ -402,11 +547,21 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           }
         }
       }
+      if (threadIdx.x == 64) stamp<TRACED>(p, 6);  // this member's slice is stored
+    } else if (!push) {
+      if (warp >= 2) {
+        const int tid = threadIdx.x - 64;
+        if (members <= 2) pull_slices_wide<EPI, 2, 4>(p, partial, members, tid, rows, r_begin, n0);
+        else if (members <= kWideSliceMembers) pull_slices_wide<EPI, kWideSliceMembers, 2>(p, partial, members, tid, rows, r_begin, n0);
+        else pull_slices_narrow<EPI>(p, partial, members, tid, rows, r_begin, n0);
+        if (threadIdx.x == 64) stamp<TRACED>(p, 6);  // this member's slice is stored
+      }
+      cluster_sync_all();  // nobody leaves while its shared memory is still being read
     }
-    cluster_sync_all();  // nobody leaves while its shared memory is still being read
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (threadIdx.x == 0) stamp<TRACED>(p, 7);  // about to leave
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(static_cast<uint32_t>(p.tmem_cols))
@@ -453,25 +608,52 @@ struct StreamPlan {
   size_t smem;
 };
 
-// The kernel's opt-ins, each asked for once (or once per larger size).
-bool allow_shared_memory(size_t bytes) {
-  static size_t allowed = 0;
-  if (bytes > allowed) {
-    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) !=
-        cudaSuccess)
-      return false;
-    allowed = bytes;
+// The kernel's instantiations. A product around a folded norm is never traced and never has more
+// than kPushTokens tokens (so its cluster never takes the pull form).
+using StreamKernel = void (*)(const CUtensorMap, const CUtensorMap, const StreamParams);
+
+template <int EPI, int MODE>
+StreamKernel pick_form(bool folded, bool traced) {
+  if constexpr (MODE != MODE_PULL) {
+    if (folded) return stream_gemm_kernel<EPI, MODE, true, false>;
   }
-  return true;
+  return traced ? stream_gemm_kernel<EPI, MODE, false, true> : stream_gemm_kernel<EPI, MODE, false, false>;
+}
+template <int EPI>
+StreamKernel pick_mode(int mode, bool folded, bool traced) {
+  switch (mode) {
+    case MODE_SINGLE: return pick_form<EPI, MODE_SINGLE>(folded, traced);
+    case MODE_PUSH: return pick_form<EPI, MODE_PUSH>(folded, traced);
+    default: return pick_form<EPI, MODE_PULL>(folded, traced);
+  }
+}
+StreamKernel pick_kernel(int epilogue, int mode, bool folded, bool traced) {
+  switch (epilogue) {
+    case EPI_F32: return pick_mode<EPI_F32>(mode, folded, traced);
+    case EPI_SWIGLU: return pick_mode<EPI_SWIGLU>(mode, folded, traced);
+    default: return pick_mode<EPI_BF16>(mode, folded, traced);
+  }
+}
+int cluster_mode(int members, int tokens_pad) {
+  return members <= 1 ? MODE_SINGLE : (tokens_pad <= kPushTokens ? MODE_PUSH : MODE_PULL);
 }
 
-bool allow_wide_clusters() {
-  static bool allowed = false;
-  if (!allowed) {
-    if (cudaFuncSetAttribute(stream_gemm_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
-      return false;
-    allowed = true;
+// An instantiation's opt-ins, asked for when it is first used: as much dynamic shared memory as
+// any plan wants, and clusters of more than eight blocks.
+constexpr size_t kMaxDynamicSmem = 200 * 1024;
+bool prepare_kernel(StreamKernel kernel) {
+  static std::mutex guard;
+  static std::vector<StreamKernel> ready;
+  std::lock_guard<std::mutex> lock(guard);
+  for (StreamKernel known : ready)
+    if (known == kernel) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxDynamicSmem)) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
   }
+  ready.push_back(kernel);
   return true;
 }
 
@@ -493,17 +675,21 @@ void size_ring(StreamPlan& plan, int k_blocks, int tokens_pad) {
   plan.stages = stages < 2 ? 2 : stages;
   const size_t partial = static_cast<size_t>(tokens_pad) * kBlockRows * sizeof(float);
   const size_t ring = plan.stages * stage;
-  plan.smem = (ring > partial ? ring : partial) + 1024;
+  if (plan.members > 1 && tokens_pad <= kPushTokens) {
+    // The inbox lies behind the ring: [members][M][slice] partial sums.
+    const int slice = slice_rows(plan.members, tokens_pad);
+    plan.smem = ring + static_cast<size_t>(plan.members) * tokens_pad * slice * sizeof(float) + 1024;
+  } else {
+    plan.smem = (ring > partial ? ring : partial) + 1024;
+  }
 }
 
 // How many clusters of `members` blocks the device holds at once when every SM takes one
 // block (clusters do not straddle GPCs, so this is less than SMs / members); 0 if the question
 // cannot be answered. Plans are remembered, so this runs once per shape.
 int clusters_one_per_sm(int members) {
-  if (!allow_shared_memory(48 * 1024) || (members > 8 && !allow_wide_clusters())) {
-    cudaGetLastError();
-    return 0;
-  }
+  const StreamKernel kernel = pick_kernel(EPI_BF16, MODE_PULL, false, false);  // the forms differ by a few registers only
+  if (!prepare_kernel(kernel)) return 0;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(1, members * 64);
   config.blockDim = dim3(kThreadsT);
@@ -516,7 +702,7 @@ int clusters_one_per_sm(int members) {
   config.attrs = &attribute;
   config.numAttrs = 1;
   int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, stream_gemm_kernel, &config) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -568,6 +754,11 @@ StreamPlan plan_stream_uncached(int N, int K, int tokens_pad) {
   return plan;
 }
 
+// Where the next launches record their blocks' timestamps (b200_stream_gemm_trace): launch i of
+// the `launches` that follow writes kTraceStamps values per block from `buffer + i * stride`.
+struct TraceTarget { long long* buffer = nullptr; int launches = 0, stride = 0, next = 0; };
+TraceTarget g_trace;
+
 // The plan is a function of N, K and the padded token count only (see gemm_skinny.cu for why
 // not of M): about two blocks per SM, each with a ring of at most half an SM's shared memory,
 // so that the blocks of the next kernel on the stream can move in and request their weights
@@ -601,6 +792,18 @@ B200_API int b200_stream_gemm_supported(int M, int N, int K, int epilogue) {
 
 // For parameter sweeps only: force the ring depth, the number of blocks aimed at or the cluster
 // width of every later plan (0 = the planner's own choice). Plans made meanwhile are not remembered.
+// A sweep's timeline (cli/microbench.py): the next `launches` launches of the kernel write eight
+// timestamps per block into `buffer` (device memory, zeroed by the caller), `stride` values
+// apart; launches whose blocks do not fit a stride, and all later ones, record nothing. Null
+// switches it off. A launch captured in a graph keeps its place at every replay.
+B200_API void b200_stream_gemm_trace(long long* buffer, int launches, int stride) {
+  g_trace.buffer = buffer;
+  g_trace.launches = buffer != nullptr ? launches : 0;
+  g_trace.stride = stride;
+  g_trace.next = 0;
+}
+B200_API int b200_stream_gemm_trace_stamps() { return kTraceStamps; }
+
 B200_API void b200_stream_gemm_plan_override(int stages, int target, int members) {
   g_plan_override.stages = stages;
   g_plan_override.target = target;
@@ -661,18 +864,30 @@ static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, 
   p.tokens_pad = (M + 15) / 16 * 16;
   p.tmem_cols = 32;
   while (p.tmem_cols < p.tokens_pad) p.tmem_cols *= 2;
-  p.epilogue = epilogue;
   p.fold = fold;
   const StreamPlan plan = plan_stream(N, K, p.tokens_pad);
   p.stages = plan.stages;
+  const bool folded = fold.ss_in != nullptr || fold.x != nullptr;
+  p.trace = nullptr;
+  if (!folded && g_trace.next < g_trace.launches && plan.blocks * plan.members * kTraceStamps <= g_trace.stride)
+    p.trace = g_trace.buffer + static_cast<int64_t>(g_trace.next++) * g_trace.stride;
   CUtensorMap w_map, x_map;
   if (make_map(&w_map, W, N, K, kBlockRows) != 0) return -1;
   if (make_map(&x_map, X, M, K, p.tokens_pad) != 0) return -1;
-  if (!allow_shared_memory(plan.smem)) return b200_fail("stream_gemm: cannot size shared memory (%zu bytes)", plan.smem);
+  const int mode = cluster_mode(plan.members, p.tokens_pad);
+  B200_REQUIRE(!(folded && (mode == MODE_PULL || p.trace != nullptr)), "stream_gemm: a folded norm with %d tokens", M);
+  B200_REQUIRE(plan.smem <= kMaxDynamicSmem, "stream_gemm: the plan wants %zu bytes of shared memory", plan.smem);
+  const StreamKernel kernel = pick_kernel(epilogue, mode, folded, p.trace != nullptr);
+  if (!prepare_kernel(kernel)) return b200_fail("stream_gemm: the kernel's attributes could not be set");
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(plan.blocks, plan.members);
   config.blockDim = dim3(kThreadsT);
-  config.dynamicSmemBytes = plan.smem;
+  // The plan reserves an inbox for a full padded step; a launch asks for its own tokens' worth, so
+  // that short steps leave more of the SM to the blocks of the kernels around them.
+  size_t smem = plan.smem;
+  if (plan.members > 1 && p.tokens_pad <= kPushTokens)
+    smem -= static_cast<size_t>(plan.members) * (p.tokens_pad - M) * slice_rows(plan.members, p.tokens_pad) * sizeof(float);
+  config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attributes[2];
   int count = 0;
@@ -690,9 +905,7 @@ static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, 
   }
   config.attrs = attributes;
   config.numAttrs = count;
-  if (plan.members > 8 && !allow_wide_clusters())
-    return b200_fail("stream_gemm: clusters of %d blocks are not available", plan.members);
-  const cudaError_t status = cudaLaunchKernelEx(&config, stream_gemm_kernel, w_map, x_map, p);
+  const cudaError_t status = cudaLaunchKernelEx(&config, kernel, w_map, x_map, p);
   if (status != cudaSuccess) return b200_fail("stream_gemm: %s", cudaGetErrorString(status));
   return 0;
 }

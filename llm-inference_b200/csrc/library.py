@@ -91,6 +91,10 @@ class KernelLibrary:
         self.lib.b200_stream_gemm_supported.restype = c_int
         self.lib.b200_stream_gemm_plan_override.argtypes = [c_int] * 3
         self.lib.b200_stream_gemm_plan_override.restype = None
+        self.lib.b200_stream_gemm_trace.argtypes = [c_void_p, c_int, c_int]
+        self.lib.b200_stream_gemm_trace.restype = None
+        self.lib.b200_stream_gemm_trace_stamps.argtypes = []
+        self.lib.b200_stream_gemm_trace_stamps.restype = c_int
         self.lib.b200_sm_count.restype = c_int
         self.lib.b200_skinny_gemm_fold_parts.argtypes = [c_int, c_int]
         self.lib.b200_skinny_gemm_fold_parts.restype = c_int
