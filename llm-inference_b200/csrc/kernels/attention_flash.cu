@@ -166,12 +166,20 @@ __device__ __forceinline__ void load_tile(unsigned char* k_dst, unsigned char* v
 // memory (`smem`, at least (kWarps + 1) * 16 * (HEAD_DIM + 2) floats that nothing else uses any
 // more); the block's result is then final (one split), handed to the merge kernel through
 // scratch, or merged with the other splits on chip when they form a thread-block cluster.
-template <int HEAD_DIM>
+// How a decode block's result leaves it: as the answer (one split), as a partial result for the
+// merge kernel, or through the cluster's shared memory. FINISH_ANY decides at run time; the
+// kernels that are compiled for one way carry no code for the others (a block runs this once,
+// from a cold instruction cache).
+enum : int { FINISH_ANY = -1, FINISH_WHOLE = 0, FINISH_PARTIAL = 1, FINISH_CLUSTER = 2 };
+
+template <int HEAD_DIM, int FINISH = FINISH_ANY>
 __device__ __forceinline__ void finish_decode_block(const FlashParams& p, unsigned char* smem,
                                                     const float (&o)[HEAD_DIM / 8][4], float m0, float l0,
                                                     float m1, float l1, int rows_total, int kv_head,
                                                     int q_start, int split) {
   constexpr int kDimTiles = HEAD_DIM / 8;
+  const bool whole = FINISH == FINISH_ANY ? p.splits == 1 : FINISH == FINISH_WHOLE;
+  const bool cluster = FINISH == FINISH_ANY ? (p.splits > 1 && p.cluster_merge) : FINISH == FINISH_CLUSTER;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col = (lane & 3) * 2;
   // Merge the four warps' partial results through shared memory (the K/V tiles are
@@ -216,9 +224,9 @@ __device__ __forceinline__ void finish_decode_block(const FlashParams& p, unsign
     const int tok = row / p.group;
     const int head = kv_head * p.group + (row - tok * p.group);
     const int64_t out_row = static_cast<int64_t>(q_start + tok) * p.q_heads + head;
-    if (p.splits == 1) {
+    if (whole) {
       p.out[out_row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    } else if (p.cluster_merge) {
+    } else if (cluster) {
       block_o[row * HEAD_DIM + d] = acc;
       if (d == 0) {
         block_ml[row * 2 + 0] = m;
@@ -232,7 +240,7 @@ __device__ __forceinline__ void finish_decode_block(const FlashParams& p, unsign
       }
     }
   }
-  if (p.splits == 1 || !p.cluster_merge) return;
+  if (!cluster) return;
 
   // The splits of this (request, kv head) are the blocks of one cluster. Each left its partial
   // result in its own shared memory; after a cluster barrier every block finishes a slice of
@@ -549,10 +557,13 @@ __host__ __device__ constexpr int merge_groups(int splits) {
   return splits <= kMaxClusterSplits * kMergeGroups ? (splits + kMaxClusterSplits - 1) / kMaxClusterSplits : 1;
 }
 
-template <int HEAD_DIM>
-__global__ void flash_merge_kernel(const float* __restrict__ partial_out,
-                                   const float* __restrict__ partial_ml,
-                                   __nv_bfloat16* __restrict__ out, int splits) {
+// FAST: at most kMaxClusterSplits splits per group of the block and a thread per head dim (the
+// launcher knows); the general form loops. Two instantiations, so that the usual one is short.
+// The partial results are written by the kernel in front while this one may already be resident
+// (programmatic dependent launch): they are not `__restrict__`, which would allow the compiler
+// to fetch them through the read-only path ahead of the wait for that kernel.
+template <int HEAD_DIM, bool FAST>
+__global__ void flash_merge_kernel(const float* partial_out, const float* partial_ml, __nv_bfloat16* out, int splits) {
   __shared__ float group_acc[kMergeGroups][HEAD_DIM];
   __shared__ float2 group_ml[kMergeGroups];
   let_successor_start();
@@ -560,7 +571,7 @@ __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
   const int64_t row = blockIdx.x;
   const float2* ml = reinterpret_cast<const float2*>(partial_ml + row * splits * 2);
   const int groups = static_cast<int>(blockDim.y);
-  if (splits <= kMaxClusterSplits * groups && HEAD_DIM <= static_cast<int>(blockDim.x)) {
+  if constexpr (FAST) {
     // Every load of this thread (its splits' maxima and sums, and its dim of each of their
     // outputs) is requested before the first is used: one round trip to L2 instead of three.
     const int d = threadIdx.x, g = threadIdx.y, base = g * kMaxClusterSplits;
@@ -600,24 +611,36 @@ __global__ void flash_merge_kernel(const float* __restrict__ partial_out,
       }
     }
     if (d < HEAD_DIM) out[row * HEAD_DIM + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-    return;
+  } else {
+    if (threadIdx.y != 0) return;
+    float m = -INFINITY;
+#pragma unroll 8
+    for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i].x);
+    const float use = m == -INFINITY ? 0.f : m;
+    float l = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < splits; ++i) l += ml[i].y * exp2f(ml[i].x - use);
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
+      float acc = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < splits; ++i)
+        acc += partial_out[(row * splits + i) * HEAD_DIM + d] * exp2f(ml[i].x - use);
+      out[row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
+    }
   }
-  if (threadIdx.y != 0) return;
-  float m = -INFINITY;
-#pragma unroll 8
-  for (int i = 0; i < splits; ++i) m = fmaxf(m, ml[i].x);
-  const float use = m == -INFINITY ? 0.f : m;
-  float l = 0.f;
-#pragma unroll 8
-  for (int i = 0; i < splits; ++i) l += ml[i].y * exp2f(ml[i].x - use);
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  for (int d = threadIdx.x; d < HEAD_DIM; d += blockDim.x) {
-    float acc = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < splits; ++i)
-      acc += partial_out[(row * splits + i) * HEAD_DIM + d] * exp2f(ml[i].x - use);
-    out[row * HEAD_DIM + d] = __float2bfloat16_rn(acc * inv);
-  }
+}
+
+// The merge kernel for `splits` splits: the fast form when the block it is launched with
+// (a thread per head dim x merge_groups(splits)) covers them.
+template <int HEAD_DIM>
+cudaError_t launch_merge(const float* partial_out, const float* partial_ml, __nv_bfloat16* out, int rows, int splits,
+                         cudaStream_t stream) {
+  const int groups = merge_groups(splits);
+  const dim3 block(HEAD_DIM <= 64 ? 64 : 128, groups);
+  if (splits <= kMaxClusterSplits * groups && HEAD_DIM <= 128)
+    return launch_kernel(flash_merge_kernel<HEAD_DIM, true>, dim3(rows), block, 0, stream, partial_out, partial_ml, out, splits);
+  return launch_kernel(flash_merge_kernel<HEAD_DIM, false>, dim3(rows), block, 0, stream, partial_out, partial_ml, out, splits);
 }
 
 // ---- decode with keys and values brought in by TMA ------------------------------------------
@@ -672,6 +695,7 @@ __device__ __forceinline__ int box_offset(int row, int chunk) {
   return (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
 }
 
+template <int FINISH>
 __global__ void __launch_bounds__(kFlashThreads)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                         const FlashParams p, const int stages) {
@@ -889,7 +913,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  finish_decode_block<kTmaDim>(p, ring, o, m0, l0, m1, l1, rows_total, kv_head, q_start, split);
+  finish_decode_block<kTmaDim, FINISH>(p, ring, o, m0, l0, m1, l1, rows_total, kv_head, q_start, split);
 }
 
 template <int HEAD_DIM>
@@ -945,9 +969,7 @@ int launch_flash(const FlashParams& p, int num_seqs, int decode, int max_q_len, 
     }
     launch_kernel(paged_flash_attention_kernel<HEAD_DIM, true>, grid, dim3(kFlashThreads), smem, stream, p);
     if (p.splits > 1) {
-      launch_kernel(flash_merge_kernel<HEAD_DIM>, dim3(tokens * p.q_heads),
-                    dim3(HEAD_DIM <= 64 ? 64 : 128, merge_groups(p.splits)), 0, stream, p.partial_out, p.partial_ml,
-                    p.out, p.splits);
+      launch_merge<HEAD_DIM>(p.partial_out, p.partial_ml, p.out, tokens * p.q_heads, p.splits, stream);
     }
   } else {
     const int row_blocks = (max_q_len * p.group + kWarps * 16 - 1) / (kWarps * 16);
@@ -1122,8 +1144,10 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
   if (decode_arena_map(&v_map, v_arena, rows) != 0) return -1;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(decode_tma_smem_bytes(kTmaMaxStages))) != cudaSuccess)
+    const int most = static_cast<int>(decode_tma_smem_bytes(kTmaMaxStages));
+    if (cudaFuncSetAttribute(paged_decode_tma_kernel<FINISH_WHOLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(paged_decode_tma_kernel<FINISH_PARTIAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess ||
+        cudaFuncSetAttribute(paged_decode_tma_kernel<FINISH_CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, most) != cudaSuccess)
       return b200_fail("decode attention (TMA): cannot size shared memory");
     configured = true;
   }
@@ -1133,7 +1157,7 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
     // The splits of a (request, kv head) form one thread-block cluster and merge on chip.
     static bool wide_clusters = false;
     if (splits > 8 && !wide_clusters) {
-      if (cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+      if (cudaFuncSetAttribute(paged_decode_tma_kernel<FINISH_CLUSTER>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
         return b200_fail("decode attention (TMA): clusters of %d blocks are not allowed here", splits);
       wide_clusters = true;
     }
@@ -1151,15 +1175,17 @@ B200_API int b200_paged_decode_attention_tma(const void* q, const void* k_arena,
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = b200_overlap_enabled() ? 2 : 1;
-    status = cudaLaunchKernelEx(&config, paged_decode_tma_kernel, k_map, v_map, p, stages);
+    status = cudaLaunchKernelEx(&config, paged_decode_tma_kernel<FINISH_CLUSTER>, k_map, v_map, p, stages);
+  } else if (splits > 1) {
+    status = launch_kernel(paged_decode_tma_kernel<FINISH_PARTIAL>, grid, dim3(kFlashThreads),
+                           decode_tma_smem_bytes(stages), stream, k_map, v_map, p, stages);
   } else {
-    status = launch_kernel(paged_decode_tma_kernel, grid, dim3(kFlashThreads), decode_tma_smem_bytes(stages), stream,
-                           k_map, v_map, p, stages);
+    status = launch_kernel(paged_decode_tma_kernel<FINISH_WHOLE>, grid, dim3(kFlashThreads),
+                           decode_tma_smem_bytes(stages), stream, k_map, v_map, p, stages);
   }
   if (status != cudaSuccess) return b200_fail("decode attention (TMA): %s", cudaGetErrorString(status));
   if (splits > 1 && !p.cluster_merge) {
-    status = launch_kernel(flash_merge_kernel<kTmaDim>, dim3(num_seqs * q_heads), dim3(128, merge_groups(splits)), 0,
-                           stream, p.partial_out, p.partial_ml, p.out, splits);
+    status = launch_merge<kTmaDim>(p.partial_out, p.partial_ml, p.out, num_seqs * q_heads, splits, stream);
     if (status != cudaSuccess) return b200_fail("decode attention (TMA) merge: %s", cudaGetErrorString(status));
   }
   return b200_check_launch("paged_decode_attention_tma");

@@ -42,6 +42,11 @@ int b200_check_launch(const char* what);
 // can fetch its weights while the kernel itself still waits for its predecessor (a successor
 // waits for the whole of its predecessor, which waited for its own, so the order of the
 // chain is kept). In a kernel launched the ordinary way both calls do nothing.
+// A pointer to anything an earlier kernel of the chain writes must not be `__restrict__` in such a
+// kernel: the qualifier promises the compiler that nothing else touches the data while the kernel
+// runs, and it then may fetch it (through the read-only path) ahead of the wait. That happened
+// to the kernel that merges the attention splits; only weights, constants and the step's
+// metadata keep the qualifier.
 __device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_successor_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

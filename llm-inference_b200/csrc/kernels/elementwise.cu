@@ -6,9 +6,9 @@
 
 // out[t, :] = table[ids[t], :]  (reference: cuda/kernels.cu:59-68, one row per block here)
 template <typename T>
-__global__ void embedding_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                        float* __restrict__ out, int hidden, int vocab,
-                                        int* __restrict__ err) {
+__global__ void embedding_gather_kernel(const T* __restrict__ table, const int* ids,
+                                        float* out, int hidden, int vocab,
+                                        int* err) {
   wait_for_predecessor();
   let_successor_start();
   const int t = blockIdx.x;
@@ -52,9 +52,9 @@ B200_API int b200_embedding_gather(const void* table, int table_dtype, const int
 constexpr int kNormCache = 8;
 
 template <typename T>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                               const float* __restrict__ weight, T* __restrict__ out,
-                               const int* __restrict__ rows, int hidden, float eps) {
+__global__ void rmsnorm_kernel(float* x, const T* delta,
+                               const float* __restrict__ weight, T* out,
+                               const int* rows, int hidden, float eps) {
   __shared__ float scratch[32];
   wait_for_predecessor();
   let_successor_start();
@@ -134,9 +134,9 @@ struct Quad<__nv_bfloat16> {
 };
 
 template <typename T>
-__global__ void rmsnorm_vec4_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                                    const float* __restrict__ weight, T* __restrict__ out,
-                                    const int* __restrict__ rows, int hidden, float eps) {
+__global__ void rmsnorm_vec4_kernel(float* x, const T* delta,
+                                    const float* __restrict__ weight, T* out,
+                                    const int* rows, int hidden, float eps) {
   __shared__ float scratch[32];
   // The weights are constants and the row list is part of the step's metadata: both are read
   // before the wait for the kernel in front. After it, everything else this thread reads (its
@@ -234,7 +234,7 @@ B200_API int b200_rmsnorm(float* x, const void* delta, const float* weight, void
 // gate and up interleaved: gu[t, 2i] is gate_i and gu[t, 2i + 1] is up_i, which is how the
 // feed-forward stores its fused gate/up matrix.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total) {
+__global__ void silu_mul_kernel(const T* gu, T* out, int64_t total) {
   wait_for_predecessor();
   let_successor_start();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -245,7 +245,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 }
 
 // bfloat16, eight outputs per thread: two 16-byte loads, one 16-byte store.
-__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out,
                                        int64_t groups) {
   wait_for_predecessor();
   let_successor_start();

@@ -71,9 +71,9 @@ __device__ __forceinline__ float block_sum_at(const float* partial, int k_splits
 // time (measured on the tcgen05 product, gemm_tcgen05.cu).
 template <int MT, int EPI, bool FOLDED>
 __global__ void __launch_bounds__(kSkinnyThreads)
-skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ X,
-                   void* __restrict__ Y, int M, int N, int K, int row_groups,
-                   float* __restrict__ scratch, int* __restrict__ counters, const void* __restrict__ next_weights,
+skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* X,
+                   void* Y, int M, int N, int K, int row_groups,
+                   float* scratch, int* counters, const void* __restrict__ next_weights,
                    long long next_bytes, const NormFold fold) {
   // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
   extern __shared__ __align__(16) unsigned char smem_raw[];

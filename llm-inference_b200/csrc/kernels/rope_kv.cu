@@ -39,16 +39,16 @@ constexpr int kWideTokens = 64;  // from this many tokens on, one block per toke
 // handles pair slot i of its head (see below), so a decode step spreads over
 // tokens * (q_heads + 2 * kv_heads) small blocks instead of one block per token.
 template <typename T>
-__global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+__global__ void rope_kv_write_kernel(const T* qkv, const float* __restrict__ bias,
                                      const float* __restrict__ inv_freq,
                                      const int* __restrict__ positions,
                                      const int* __restrict__ token_seq,
                                      const int* __restrict__ seq_kv_len,
                                      const int* __restrict__ block_table, int max_pages,
-                                     int num_pages, T* __restrict__ k_arena,
-                                     T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
+                                     int num_pages, T* k_arena,
+                                     T* v_arena, T* q_out, int q_heads,
                                      int kv_heads, int head_dim, int rot, int page_size,
-                                     int write_kv, int* __restrict__ err) {
+                                     int write_kv, int* err) {
   let_successor_start();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0 .. q_heads + 2 * kv_heads
@@ -161,16 +161,16 @@ struct Pair<__nv_bfloat16> {
 };
 
 template <typename T>
-__global__ void rope_kv_write_wide_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+__global__ void rope_kv_write_wide_kernel(const T* qkv, const float* __restrict__ bias,
                                           const float* __restrict__ inv_freq,
                                           const int* __restrict__ positions,
                                           const int* __restrict__ token_seq,
                                           const int* __restrict__ seq_kv_len,
                                           const int* __restrict__ block_table, int max_pages,
-                                          int num_pages, T* __restrict__ k_arena,
-                                          T* __restrict__ v_arena, T* __restrict__ q_out, int q_heads,
+                                          int num_pages, T* k_arena,
+                                          T* v_arena, T* q_out, int q_heads,
                                           int kv_heads, int head_dim, int page_size, int write_kv,
-                                          int* __restrict__ err) {
+                                          int* err) {
   extern __shared__ float angles[];  // cos[half], sin[half]
   wait_for_predecessor();
   let_successor_start();

@@ -31,8 +31,8 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-argmax_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
-                   const int* __restrict__ row_index, int* __restrict__ out) {
+argmax_rows_kernel(const float* logits, int vocab, int64_t row_stride,
+                   const int* row_index, int* out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   wait_for_predecessor();
@@ -78,8 +78,8 @@ argmax_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stri
 constexpr int kArgmaxSliceThreads = 256;
 
 __global__ void __launch_bounds__(kArgmaxSliceThreads)
-argmax_slices_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, const int* __restrict__ row_index,
-                     int* __restrict__ out, unsigned long long* __restrict__ best, int* __restrict__ arrived) {
+argmax_slices_kernel(const float* logits, int vocab, int64_t row_stride, const int* row_index,
+                     int* out, unsigned long long* best, int* arrived) {
   __shared__ unsigned long long block_best[kArgmaxSliceThreads / 32];
   wait_for_predecessor();
   let_successor_start();
@@ -114,7 +114,7 @@ argmax_slices_kernel(const float* __restrict__ logits, int vocab, int64_t row_st
 }
 
 // The key of the k-th largest element (1-based), found byte by byte from the top.
-__device__ uint32_t kth_largest_key(const float* __restrict__ row, int vocab, int k,
+__device__ uint32_t kth_largest_key(const float* row, int vocab, int k,
                                     unsigned int* hist /* [256] shared */) {
   uint32_t prefix = 0, mask = 0;
   int remaining = k;
@@ -144,7 +144,7 @@ __device__ uint32_t kth_largest_key(const float* __restrict__ row, int vocab, in
 
 // Key K such that keeping keys >= K keeps exactly the candidates whose strictly-larger mass
 // is below `limit` (fixed-point). Only keys >= `floor_key` are candidates.
-__device__ uint32_t top_p_key(const float* __restrict__ row, int vocab, float inv_temp,
+__device__ uint32_t top_p_key(const float* row, int vocab, float inv_temp,
                               float scaled_max, uint32_t floor_key, unsigned long long limit,
                               unsigned long long* mass /* [256] shared */) {
   uint32_t prefix = 0, mask = 0;
@@ -179,11 +179,11 @@ __device__ uint32_t top_p_key(const float* __restrict__ row, int vocab, float in
 
 // One row, the whole vocabulary scanned by one block in every pass: what a row falls back to
 // when the faster path below cannot hold its candidates, and the only path without scratch.
-__device__ void sample_row_by_one_block(const float* __restrict__ logits, int vocab, int64_t row_stride,
-                                        const float* __restrict__ temperature, const float* __restrict__ top_p,
-                                        const float* __restrict__ min_p, const int* __restrict__ top_k,
-                                        const unsigned long long* __restrict__ keys, const int* __restrict__ row_index,
-                                        int* __restrict__ out, float* scratch /* [32] */, unsigned int* hist /* [256] */,
+__device__ void sample_row_by_one_block(const float* logits, int vocab, int64_t row_stride,
+                                        const float* temperature, const float* top_p,
+                                        const float* min_p, const int* top_k,
+                                        const unsigned long long* keys, const int* row_index,
+                                        int* out, float* scratch /* [32] */, unsigned int* hist /* [256] */,
                                         unsigned long long* mass /* [256] */, float* partial /* [kSampleThreads] */,
                                         int* chosen_slot) {
   int& chosen = *chosen_slot;
@@ -288,11 +288,11 @@ __device__ void sample_row_by_one_block(const float* __restrict__ logits, int vo
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-sample_rows_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
-                   const float* __restrict__ temperature, const float* __restrict__ top_p,
-                   const float* __restrict__ min_p, const int* __restrict__ top_k,
-                   const unsigned long long* __restrict__ keys, const int* __restrict__ row_index,
-                   int* __restrict__ out) {
+sample_rows_kernel(const float* logits, int vocab, int64_t row_stride,
+                   const float* temperature, const float* top_p,
+                   const float* min_p, const int* top_k,
+                   const unsigned long long* keys, const int* row_index,
+                   int* out) {
   __shared__ float scratch[32];
   __shared__ unsigned int hist[256];
   __shared__ unsigned long long mass[256];
@@ -330,8 +330,8 @@ struct RowScratch {
 };
 
 __global__ void __launch_bounds__(kSliceThreads)
-select_pass_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride, const int* __restrict__ row_index,
-                   RowScratch* __restrict__ rows, int shift) {
+select_pass_kernel(const float* logits, int vocab, int64_t row_stride, const int* row_index,
+                   RowScratch* rows, int shift) {
   __shared__ unsigned int local[256];
   wait_for_predecessor();
   let_successor_start();
@@ -377,8 +377,8 @@ select_pass_kernel(const float* __restrict__ logits, int vocab, int64_t row_stri
 }
 
 __global__ void __launch_bounds__(kSliceThreads)
-collect_candidates_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
-                          const int* __restrict__ row_index, RowScratch* __restrict__ rows) {
+collect_candidates_kernel(const float* logits, int vocab, int64_t row_stride,
+                          const int* row_index, RowScratch* rows) {
   wait_for_predecessor();
   let_successor_start();
   RowScratch& mine = rows[blockIdx.y];
@@ -450,11 +450,11 @@ __device__ void block_prefix_sums(float* value, int n, float* warp_totals /* [32
 }
 
 __global__ void __launch_bounds__(kSampleThreads)
-sample_from_candidates_kernel(const float* __restrict__ logits, int vocab, int64_t row_stride,
-                              const float* __restrict__ temperature, const float* __restrict__ top_p,
-                              const float* __restrict__ min_p, const int* __restrict__ top_k,
-                              const unsigned long long* __restrict__ keys, const int* __restrict__ row_index,
-                              int* __restrict__ out, RowScratch* __restrict__ rows, int direct) {
+sample_from_candidates_kernel(const float* logits, int vocab, int64_t row_stride,
+                              const float* temperature, const float* top_p,
+                              const float* min_p, const int* top_k,
+                              const unsigned long long* keys, const int* row_index,
+                              int* out, RowScratch* rows, int direct) {
   // The fallback's shared memory and the list's are never live together.
   __shared__ float scratch[32];
   __shared__ unsigned int hist[256];
