@@ -422,7 +422,7 @@ def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = Fal
     kernel (three blocks per SM) wants about two waves of blocks. The TMA kernel (rings three
     deep, two blocks per SM) wants all its blocks resident at once: measured on a B200 at
     2,048 keys, 64 requests x 2 kv heads take 26 us in 2 splits and 35 us in 6, and 64 x 8
-    take 82 us unsplit. Normally at most 16 splits. Very few pairs with many keys go up to 64
+    take 82 us unsplit. Normally at most 16 splits (14 or fewer for 10 to 24 pairs of up to 4,096 keys, see below). Very few pairs with many keys go up to 64
     while every split keeps four tiles: one request of the 1.5B shape with 30,000 keys is 32
     blocks for 148 SMs in 16 splits (1.94 ms per step) and 128 blocks in 64 (1.35 ms); 8,192
     keys: 1.36 -> 1.15 ms. With 8 such requests 18 splits were no faster than 16 (2.26 vs
@@ -430,7 +430,21 @@ def decode_splits(num_seqs: int, kv_heads: int, max_kv_len: int, tma: bool = Fal
     tiles = max(1, (max_kv_len + 63) // 64)
     pairs = max(1, num_seqs * kv_heads)
     want = (2 if tma else 6) * num_sms // pairs  # rounded down: one block too many would start another wave
-    most = 16 if want < 32 else max(16, min(MAX_DECODE_SPLITS, tiles // 4))
+    if want >= 32:
+        most = max(16, min(MAX_DECODE_SPLITS, tiles // 4))
+    elif tma and want >= 12 and tiles <= 64:
+        # 10 to 24 pairs of up to 4,096 keys: the blocks share their SMs with the kernels around them in the chain, and
+        # about 1.5 blocks per SM leave those room to move in early. Measured at 2,100-2,300 keys,
+        # 1.5B shape, ms per step with 16 (or the 2-per-SM count) -> with this rule: batch 5 1.125 ->
+        # 1.115, 6 1.131 -> 1.121, 7 1.137 -> 1.131, 8 1.153 -> 1.132 (1,200 keys 1.112 -> 1.090,
+        # 3,800 keys 1.217 -> 1.199), 9 1.273 -> 1.268, 10 1.282 -> 1.264, 12 unchanged; 7B shape,
+        # batch 4: 2.722 -> 2.686. With more pairs (batch 16: 9 splits, 32: 4, 64: 2) two per SM
+        # stay the best, with fewer (batch 4: 16 or 20 splits) the blocks do not fill the SMs; with
+        # more keys the attention wants the SMs for itself (batch 8, 8,192 keys: 1.353 ms with 16
+        # splits, 1.378 with 13; 30,000 keys: 2.097 and 2.136).
+        most = min(14, (3 * num_sms // 2) // pairs)
+    else:
+        most = 16
     return max(1, min(tiles, most, want))
 
 

@@ -102,8 +102,9 @@ def test_how_decode_attention_cuts_the_key_range():
                     assert 1 <= splits <= min(MAX_DECODE_SPLITS, (keys + 63) // 64)
                     if keys <= 4096:
                         assert splits <= 16
-    assert decode_splits(1, 2, 4096, True) == 16 and decode_splits(8, 2, 4096, True) == 16
+    assert decode_splits(1, 2, 4096, True) == 16 and decode_splits(8, 2, 4096, True) == 13  # 222 blocks / 16 pairs
     assert decode_splits(1, 2, 32768, True) == 64 and decode_splits(8, 2, 32768, True) == 16
+    assert decode_splits(6, 2, 4096, True) == 14 and decode_splits(16, 2, 4096, True) == 9  # 296 / 32
     assert decode_splits(1, 8, 32768, True) == 37  # 296 resident blocks / 8 pairs
     assert decode_splits(64, 2, 2048, True) == 2 and decode_splits(64, 8, 2048, True) == 1
     assert decode_splits(1, 2, 100, True) == 2
