@@ -295,7 +295,6 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=0, help="longest request the engine is built for (default: twice the prompt)")
     parser.add_argument("--no-graphs", action="store_true")
     parser.add_argument("--fold-norms", action="store_true", help="fold the norms of short steps into the products around them")
-    parser.add_argument("--weight-prefetch", type=int, default=0, help="decode products fetch into L2 the weights of the product N places ahead")
     parser.add_argument("--decode-kernel", choices=["chain", "resident"], default="chain",
                         help="'resident': time the one-kernel decode step instead of the chain of kernels")
     args = parser.parse_args()
@@ -355,7 +354,7 @@ def main() -> int:
     engine = Engine(
         model=model, max_num_sequences=max_batch, max_model_length=context, kv_cache_bytes=budget_tokens * kv_bytes_per_token,
         page_size=PAGE, prefill_chunk_size=PROMPT, prefill_burst_size=PROMPT, max_batch_tokens=PROMPT + max_batch,
-        cuda_graphs=not args.no_graphs, decode_kernel=args.decode_kernel, weight_prefetch=args.weight_prefetch, fold_norms=args.fold_norms,
+        cuda_graphs=not args.no_graphs, decode_kernel=args.decode_kernel, fold_norms=args.fold_norms,
     )
     runner, cache = engine.runner, engine.cache
     rng = np.random.default_rng(0)

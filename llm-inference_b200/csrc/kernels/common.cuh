@@ -50,25 +50,6 @@ int b200_check_launch(const char* what);
 __device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void let_successor_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Asks the memory system to bring `bytes` starting at `base` into the L2 cache; each block of
-// the grid requests its own slice (thread 0, in pieces of 32 KB). Fire and forget: used by a
-// matrix product to fetch the weights of the product that follows it on the stream while
-// its own latency-bound phases leave HBM idle.
-__device__ __forceinline__ void prefetch_slice_to_l2(const void* base, long long bytes) {
-  if (base == nullptr || bytes <= 0 || threadIdx.x != 0) return;
-  const long long blocks = static_cast<long long>(gridDim.x) * gridDim.y * gridDim.z;
-  const long long block = (static_cast<long long>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
-  long long slice = (bytes + blocks - 1) / blocks;
-  slice = (slice + 4095) & ~4095LL;
-  const long long begin = block * slice;
-  const long long end = begin + slice < bytes ? begin + slice : (bytes & ~15LL);
-  const char* p = static_cast<const char*>(base);
-  for (long long at = begin; at < end; at += 32768) {
-    const unsigned int piece = static_cast<unsigned int>(end - at < 32768 ? end - at : 32768);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + at), "r"(piece) : "memory");
-  }
-}
-
 // Thread-block clusters: a barrier over every thread of every block of the cluster, and a
 // 32-bit load from the same shared-memory address in another block of the cluster.
 __device__ __forceinline__ void cluster_sync_all() {
@@ -95,11 +76,16 @@ __device__ __forceinline__ float4 load_peer_f32x4(const float* local, uint32_t r
                : "memory");
   return v;
 }
-__device__ __forceinline__ void store_peer_f32(float* local, uint32_t rank, float v) {
+// The address, in the cluster's shared-memory window, of `local` in block `rank`; and a 32-bit
+// store to such an address plus a byte offset.
+__device__ __forceinline__ uint32_t peer_address(const void* local, uint32_t rank) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
                : "=r"(remote)
                : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(local))), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void store_peer_f32(uint32_t remote, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 

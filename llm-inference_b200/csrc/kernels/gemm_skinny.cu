@@ -73,8 +73,7 @@ template <int MT, int EPI, bool FOLDED>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* X,
                    void* Y, int M, int N, int K, int row_groups,
-                   float* scratch, int* counters, const void* __restrict__ next_weights,
-                   long long next_bytes, const NormFold fold) {
+                   float* scratch, int* counters, const NormFold fold) {
   // Ring: [warp][stage][piece][lane] of 16-byte pieces; piece 0/1 = W rows g / g + 8, 2.. = X.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint4* ring = reinterpret_cast<uint4*>(smem_raw);
@@ -121,13 +120,13 @@ skinny_gemm_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* X,
 
   let_successor_start();
   // Weights do not depend on the previous kernel: request them first, then wait for it.
-#pragma unroll
+  // Rolled on purpose, like the loop over X below: unrolled, the two took 5 KB of the kernel's 24.
+#pragma unroll 1
   for (int i = 0; i < kStages; ++i) fetch_w(c_begin + i, i);
   copy_async_commit();
-  prefetch_slice_to_l2(next_weights, next_bytes);
   wait_for_predecessor();
   let_successor_start();
-#pragma unroll
+#pragma unroll 1
   for (int i = 0; i < kStages; ++i) fetch_x(c_begin + i, i);
   copy_async_commit();
   if (FOLDED && fold.ss_in != nullptr) {
@@ -286,7 +285,7 @@ SkinnyPlan plan_skinny(int N, int K) {
 template <int MT, int EPI, bool FOLDED>
 int launch_skinny_as(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
                      const SkinnyPlan& plan, float* scratch, int* counters, cudaStream_t stream,
-                     const void* next_weights, long long next_bytes, bool ordered, const NormFold& fold) {
+                     bool ordered, const NormFold& fold) {
   const int block_rows = plan.row_groups * 16;
   const int k_splits = kSkinnyWarps / plan.row_groups;
   const size_t ring = static_cast<size_t>(kSkinnyWarps) * SkinnyStages<MT>::value * (2 + MT) * 32 * 16;
@@ -305,8 +304,7 @@ int launch_skinny_as(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, in
   }
   const dim3 grid(plan.blocks, plan.column_blocks);
   cudaError_t status = launch_kernel_as(ordered, skinny_gemm_kernel<MT, EPI, FOLDED>, grid, dim3(kSkinnyThreads), smem,
-                                        stream, W, X, Y, M, N, K, plan.row_groups, scratch, counters, next_weights,
-                                        next_bytes, fold);
+                                        stream, W, X, Y, M, N, K, plan.row_groups, scratch, counters, fold);
   if (status != cudaSuccess) return b200_fail("skinny_gemm: %s", cudaGetErrorString(status));
   return 0;
 }
@@ -314,29 +312,24 @@ int launch_skinny_as(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, in
 template <int MT, int EPI>
 int launch_skinny_epilogue(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
                            const SkinnyPlan& plan, float* scratch, int* counters, cudaStream_t stream,
-                           const void* next_weights, long long next_bytes, bool ordered, const NormFold& fold) {
+                           bool ordered, const NormFold& fold) {
   if (fold.ss_in != nullptr || fold.x != nullptr)
-    return launch_skinny_as<MT, EPI, true>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights, next_bytes,
-                                           ordered, fold);
-  return launch_skinny_as<MT, EPI, false>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights, next_bytes,
-                                          ordered, fold);
+    return launch_skinny_as<MT, EPI, true>(W, X, Y, M, N, K, plan, scratch, counters, stream, ordered, fold);
+  return launch_skinny_as<MT, EPI, false>(W, X, Y, M, N, K, plan, scratch, counters, stream, ordered, fold);
 }
 
 template <int MT>
 int launch_skinny(const __nv_bfloat16* W, const __nv_bfloat16* X, void* Y, int M, int N, int K,
                   const SkinnyPlan& plan, int epilogue, float* scratch, int* counters, cudaStream_t stream,
-                  const void* next_weights = nullptr, long long next_bytes = 0, bool ordered = false,
+                  bool ordered = false,
                   const NormFold& fold = NormFold{}) {
   switch (epilogue) {
     case EPI_F32:
-      return launch_skinny_epilogue<MT, EPI_F32>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
-                                                 next_bytes, ordered, fold);
+      return launch_skinny_epilogue<MT, EPI_F32>(W, X, Y, M, N, K, plan, scratch, counters, stream, ordered, fold);
     case EPI_SWIGLU:
-      return launch_skinny_epilogue<MT, EPI_SWIGLU>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
-                                                    next_bytes, ordered, fold);
+      return launch_skinny_epilogue<MT, EPI_SWIGLU>(W, X, Y, M, N, K, plan, scratch, counters, stream, ordered, fold);
     default:
-      return launch_skinny_epilogue<MT, EPI_BF16>(W, X, Y, M, N, K, plan, scratch, counters, stream, next_weights,
-                                                  next_bytes, ordered, fold);
+      return launch_skinny_epilogue<MT, EPI_BF16>(W, X, Y, M, N, K, plan, scratch, counters, stream, ordered, fold);
   }
 }
 
@@ -368,16 +361,13 @@ B200_API void b200_skinny_gemm_scratch(int M, int N, int K, int64_t* floats, int
 B200_API int b200_skinny_gemm_fold_parts(int N, int K) { return plan_skinny(N, K).blocks; }
 
 static int skinny_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, float* scratch,
-                           int64_t scratch_floats, int* counters, int num_counters, const void* next_weights,
-                           int64_t next_bytes, const NormFold& fold, cudaStream_t stream);
+                           int64_t scratch_floats, int* counters, int num_counters, const NormFold& fold,
+                           cudaStream_t stream);
 
-// `next_weights` / `next_bytes` (may be null / 0): memory the kernel asks the L2 cache to fetch
-// while it runs, meant for the weights of the product that follows on the stream.
 B200_API int b200_skinny_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue,
                               float* scratch, int64_t scratch_floats, int* counters, int num_counters,
-                              const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
-  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, next_weights,
-                         next_bytes, NormFold{}, stream);
+                              cudaStream_t stream) {
+  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, NormFold{}, stream);
 }
 
 // The same product around a folded RMSNorm (NormFold in common.cuh). With `ss_in` the operand X is
@@ -403,13 +393,12 @@ B200_API int b200_skinny_gemm_fold(const void* W, const void* X, void* Y, int M,
   B200_REQUIRE(x == nullptr || (next_weight != nullptr && xn != nullptr && ss_out != nullptr && epilogue == EPI_BF16),
                "skinny_gemm_fold: the residual epilogue needs the next norm's scale, xn and ss_out");
   B200_REQUIRE(x != nullptr || Y != nullptr, "skinny_gemm_fold: no output");
-  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, nullptr, 0, fold,
-                         stream);
+  return skinny_gemm_run(W, X, Y, M, N, K, epilogue, scratch, scratch_floats, counters, num_counters, fold, stream);
 }
 
 static int skinny_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, float* scratch,
-                           int64_t scratch_floats, int* counters, int num_counters, const void* next_weights,
-                           int64_t next_bytes, const NormFold& fold, cudaStream_t stream) {
+                           int64_t scratch_floats, int* counters, int num_counters, const NormFold& fold,
+                           cudaStream_t stream) {
   B200_REQUIRE(b200_skinny_gemm_supported(M, N, K, epilogue), "skinny_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "skinny_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -424,8 +413,8 @@ static int skinny_gemm_run(const void* W, const void* X, void* Y, int M, int N, 
   const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
   if (M <= 8)
-    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes, false, fold);
-  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, next_weights, next_bytes, false, fold);
+    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, false, fold);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, scratch, counters, stream, false, fold);
 }
 
 // ---- the variant that allocates nothing (declared and documented in gemm_skinny_static.h) ----
@@ -507,6 +496,6 @@ B200_API int b200_skinny_gemm_static(const void* W, const void* X, void* Y, int 
   // Launched the ordinary way (no programmatic overlap with the kernel before it): a caller's W may
   // be the output of that kernel, and this kernel requests its first slabs of W before it would wait.
   if (M <= 8)
-    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, nullptr, 0, true);
-  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, nullptr, 0, true);
+    return launch_skinny<1>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, true);
+  return launch_skinny<2>(w, x, Y, M, N, K, plan, epilogue, mine.scratch, mine.counters, stream, true);
 }

@@ -142,8 +142,6 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[16]) {
 struct StreamParams {
   void* y;
   int* err;
-  const void* next_weights;  // fetched into L2 while this product runs (may be null)
-  long long next_bytes;
   int stages;
   int M, N, K;
   int tokens_pad;  // MMA N: M rounded up to a multiple of 16
@@ -342,7 +340,6 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_shared;
 
-  prefetch_slice_to_l2(p.next_weights, p.next_bytes);
   if (warp == 0 && lane == 0) {
     // ---- TMA producer -----------------------------------------------------------------------
     // The weights of the first stages went out above; X follows the dependency wait.
@@ -444,10 +441,12 @@ stream_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       }
       if (push) {
         const int owner = row / slice;
-        float* mine = inbox + (static_cast<int>(blockIdx.y) * p.M + c0) * slice + (row - owner * slice);
+        const uint32_t mine =
+            peer_address(inbox + (static_cast<int>(blockIdx.y) * p.M + c0) * slice + (row - owner * slice), owner);
+        const uint32_t pitch = static_cast<uint32_t>(slice) * sizeof(float);
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          if (c0 + i < p.M) store_peer_f32(mine + i * slice, owner, v[i]);
+          if (c0 + i < p.M) store_peer_f32(mine + i * pitch, v[i]);
       } else if (clustered) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) partial[(c0 + i) * kBlockRows + row] = v[i];
@@ -811,11 +810,11 @@ B200_API void b200_stream_gemm_plan_override(int stages, int target, int members
 }
 
 static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
-                           const void* next_weights, int64_t next_bytes, const NormFold& fold, cudaStream_t stream);
+                           const NormFold& fold, cudaStream_t stream);
 
 B200_API int b200_stream_gemm(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
-                              const void* next_weights, int64_t next_bytes, cudaStream_t stream) {
-  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, next_weights, next_bytes, NormFold{}, stream);
+                              cudaStream_t stream) {
+  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, NormFold{}, stream);
 }
 
 // With a folded norm behind it (NormFold in common.cuh): how many rows of partial sums of squares a
@@ -844,11 +843,11 @@ B200_API int b200_stream_gemm_fold(const void* W, const void* X, void* Y, int M,
   B200_REQUIRE(x == nullptr || (next_weight != nullptr && xn != nullptr && ss_out != nullptr && epilogue == EPI_BF16),
                "stream_gemm_fold: the residual epilogue needs the next norm's scale, xn and ss_out");
   B200_REQUIRE(x != nullptr || Y != nullptr, "stream_gemm_fold: no output");
-  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, nullptr, 0, fold, stream);
+  return stream_gemm_run(W, X, Y, M, N, K, epilogue, err, fold, stream);
 }
 
 static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, int K, int epilogue, int* err,
-                           const void* next_weights, int64_t next_bytes, const NormFold& fold, cudaStream_t stream) {
+                           const NormFold& fold, cudaStream_t stream) {
   B200_REQUIRE(b200_stream_gemm_supported(M, N, K, epilogue), "stream_gemm: unsupported shape %d x %d x %d", M, N, K);
   B200_REQUIRE(epilogue >= EPI_BF16 && epilogue <= EPI_SWIGLU, "stream_gemm: unknown epilogue %d", epilogue);
   B200_REQUIRE(reinterpret_cast<uintptr_t>(W) % 16 == 0 && reinterpret_cast<uintptr_t>(X) % 16 == 0,
@@ -856,8 +855,6 @@ static int stream_gemm_run(const void* W, const void* X, void* Y, int M, int N, 
   StreamParams p;
   p.y = Y;
   p.err = err;
-  p.next_weights = next_weights;
-  p.next_bytes = next_bytes;
   p.M = M;
   p.N = N;
   p.K = K;

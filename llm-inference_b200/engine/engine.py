@@ -102,7 +102,6 @@ class Engine:
         kernels: str = "tuned",
         decode_kernel: str = "chain",
         fold_norms: bool = False,
-        weight_prefetch: int = 0,
         nvtx: bool = False,
         step_timing: bool = False,
         model: Model | None = None,
@@ -163,9 +162,6 @@ class Engine:
                 # Norms folded into the products around them in short steps (parts/ops.py::fold_enabled):
                 # fewer launches, measured no faster; an option.
                 "fold_norms": bool(fold_norms) and kernels != "plain",
-                # n > 0: every weight-streaming product of a decode step asks the L2 cache for the
-                # weights of the product n places after it in the step, while it runs.
-                "weight_prefetch": int(weight_prefetch),
                 **({"attention": "plain", "gemm": "library"} if kernels == "plain" else {}),
             },
         )

@@ -341,21 +341,7 @@ class ModelRunner:
         cached = self._graphs.get((bucket, reach))
         if cached is None:
             calls_before = self.lib.calls
-            learn = self.options.get("weight_prefetch", False) and "gemm_next" not in self.options
-            if learn:
-                self.options["gemm_trace"] = []
             logits = self.model.forward(ctx, lambda call: self._view(call, tables))
-            if learn:
-                # Which weights each matrix product of a decode step is followed by (the last one
-                # by the first of the next step): with options["weight_prefetch"] the kernels ask
-                # the L2 cache for them. Off by default: measured on a B200 at the 1.5B shape it
-                # does not shorten the step (1.70 ms with, 1.67 ms without), because these
-                # products are bound by fixed per-kernel cost, not by HBM.
-                trace = self.options.pop("gemm_trace")
-                ahead = max(1, int(self.options.get("weight_prefetch", 1)))
-                self.options["gemm_next"] = {
-                    here[0]: trace[(i + ahead) % len(trace)] for i, here in enumerate(trace)
-                } if len({t[0] for t in trace}) == len(trace) else {}
             self.launches_per_graph[bucket] = self.lib.calls - calls_before
             if self._graph_generation != self.workspace.generation:
                 # The eager run allocated scratch; capture on the next step, when nothing moves.

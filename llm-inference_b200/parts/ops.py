@@ -241,7 +241,7 @@ def _small_gemm(
     the tcgen05 kernel reduces inside its clusters and needs none. ``scale``: the operand is a
     folded norm's ``xn`` and the outputs take the tokens' 1 / rms; ``sink``: (stream, next norm's
     scale, xn, ss) for the residual epilogue (see NormFold in csrc/kernels/common.cuh)."""
-    from ctypes import byref, c_void_p
+    from ctypes import byref
 
     m, k = x.shape
     n = weight.shape[0]
@@ -254,22 +254,11 @@ def _small_gemm(
             ptr(scale.ss if scale is not None else None), c_int(scale.parts if scale is not None else 0), c_int(width),
             c_float(eps),
         ] + ([ptr(t) for t in sink] if sink is not None else [ptr(None)] * 4)
-        prefetch = []
     else:
-        # The weights of the product that follows this one in the step, if the runner has learnt the
-        # order: this kernel asks the L2 cache to fetch them while it runs.
-        trace = ctx.options.get("gemm_trace")
-        if trace is not None:
-            trace.append((weight.data_ptr(), weight.numel() * weight.element_size()))
-        upcoming = ctx.options.get("gemm_next", {}).get(weight.data_ptr())
-        if upcoming is not None:
-            prefetch = [c_void_p(upcoming[0]), c_int64(min(upcoming[1], ctx.options.get("prefetch_bytes", 64 << 20)))]
-        else:
-            prefetch = [ptr(None), c_int64(0)]
         fold = []
     suffix = "_fold" if folding else ""
     if kernel == "stream":
-        ctx.lib.call("b200_stream_gemm" + suffix, *head, ptr(ctx.err), *prefetch, *fold, ctx.stream)
+        ctx.lib.call("b200_stream_gemm" + suffix, *head, ptr(ctx.err), *fold, ctx.stream)
         return
     need = _SKINNY_SCRATCH.get((m, n, k))
     if need is None:
@@ -283,7 +272,7 @@ def _small_gemm(
         counter_buf = ctx.workspace.zeros("gemm_counters", max(counters, 4096), torch.int32)
     ctx.lib.call(
         "b200_skinny_gemm" + suffix, *head, ptr(scratch), c_int64(floats), ptr(counter_buf),
-        c_int(counter_buf.numel() if counter_buf is not None else 0), *prefetch, *fold, ctx.stream,
+        c_int(counter_buf.numel() if counter_buf is not None else 0), *fold, ctx.stream,
     )
 
 

@@ -26,7 +26,7 @@ def library():
     lib.b200_skinny_gemm_static.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.b200_skinny_gemm_static.restype = c_int
     lib.b200_skinny_gemm_static_capacity_floats.restype = ctypes.c_longlong
-    lib.b200_skinny_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_int64, c_void_p]
+    lib.b200_skinny_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]
     lib.b200_skinny_gemm.restype = c_int
     lib.b200_skinny_gemm_scratch.argtypes = [c_int, c_int, c_int, ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]
     lib.b200_skinny_gemm_scratch.restype = None
@@ -44,7 +44,7 @@ def existing_entry_point(lib, w, x, out, epilogue):
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     status = lib.b200_skinny_gemm(
         c_void_p(w.data_ptr()), c_void_p(x.data_ptr()), c_void_p(out.data_ptr()), m, n, k, epilogue,
-        c_void_p(scratch.data_ptr()), c_int64(scratch.numel()), c_void_p(counter.data_ptr()), counter.numel(), c_void_p(0), c_int64(0), stream,
+        c_void_p(scratch.data_ptr()), c_int64(scratch.numel()), c_void_p(counter.data_ptr()), counter.numel(), stream,
     )
     assert status == 0, lib.b200_last_error().decode()
     return floats.value
