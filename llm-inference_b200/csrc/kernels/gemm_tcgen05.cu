@@ -12,10 +12,11 @@
 // predecessor on the stream (programmatic dependent launch), since weights never depend on it.
 //
 // When W has too few rows to give every SM a block, the blocks that share rows form a
-// thread-block cluster and split K among them: each leaves its partial tile in its own shared
-// memory, and after a cluster barrier every block adds a slice of the rows over all members
-// in rank order through distributed shared memory, so the sum does not depend on timing and
-// no global scratch is needed.
+// thread-block cluster and split K among them. Every member finishes a slice of the rows, adding
+// the members' partial sums in rank order through distributed shared memory, so the sum does
+// not depend on timing and no global scratch is needed: with up to 16 tokens the members write
+// their partial sums into the owners' shared memory and the cluster meets once, with more they
+// keep their tiles, meet, fetch their slices from each other and meet again (see the kernel).
 //
 // Every wait on an mbarrier is bounded: on a timeout the block records ERRBIT_TIMEOUT in the
 // error word, stops issuing work, frees its TMEM and returns.
