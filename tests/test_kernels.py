@@ -158,7 +158,9 @@ def test_silu_mul(lib, dtype):
 @pytest.mark.parametrize(
     "m,n,k",
     [(1, 2048, 1536), (8, 1536, 8960), (5, 311, 96), (16, 272, 96), (9, 100, 64), (13, 4608, 3584), (8, 50, 40),
-     (2, 3000, 264), (16, 151936, 64), (3, 1536, 1536), (8, 3584, 18944)],
+     (2, 3000, 264), (16, 151936, 64), (3, 1536, 1536), (8, 3584, 18944),
+     # clusters whose last row block is ragged (8 blocks x 16 members, 104 rows in the last), 7 and all 16 tokens
+     (7, 1000, 4096), (16, 1000, 4096)],
 )
 @pytest.mark.parametrize("kernel", ["skinny", "tcgen05"])
 def test_weight_streaming_gemm_matches_float64(lib, m, n, k, kernel):
@@ -194,7 +196,9 @@ def test_weight_streaming_gemm_matches_float64(lib, m, n, k, kernel):
     assert int(ctx.err.item()) == 0
 
 
-@pytest.mark.parametrize("m,n,k", [(17, 1536, 1536), (64, 17920, 1536), (100, 272, 96), (256, 2048, 1536), (33, 1536, 8960)])
+@pytest.mark.parametrize("m,n,k", [(17, 1536, 1536), (64, 17920, 1536), (100, 272, 96), (256, 2048, 1536), (33, 1536, 8960),
+                                   # clusters of 3 (slices of 44, 44 and 40 rows, four rows per load) and of 16 with a ragged last block
+                                   (20, 10200, 1536), (40, 1000, 4096)])
 def test_tcgen05_gemm_takes_up_to_256_rows(lib, m, n, k):
     from llm_inference_b200.parts import ops
 
