@@ -218,6 +218,45 @@ def test_tcgen05_gemm_takes_up_to_256_rows(lib, m, n, k):
     assert int(ctx.err.item()) == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 1536, 8960), (40, 2048, 1536), (5, 311, 96)])  # pushed, fetched, no cluster
+def test_traced_tcgen05_gemm_gives_the_same_product_and_ordered_timestamps(lib, m, n, k):
+    """The instantiation that records a block's timestamps (cli/microbench.py --trace): the product
+    itself is unchanged, every block wrote its points, and they follow one another in time."""
+    from llm_inference_b200.csrc.library import ptr
+    from llm_inference_b200.parts import ops
+
+    torch.manual_seed(n + k)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") / math.sqrt(k)).to(torch.bfloat16)
+    ctx = make_ctx(lib, positions=[0] * m)
+    ctx.options["gemm"] = "tcgen05"
+    plain = torch.empty(m, n, device="cuda", dtype=torch.float32)
+    ops.linear(ctx, x, w, plain)
+    stamps = lib.lib.b200_stream_gemm_trace_stamps()
+    stride = 4096 * stamps
+    buffer = torch.zeros(1, stride, dtype=torch.int64, device="cuda")
+    lib.lib.b200_stream_gemm_trace(ptr(buffer), 1, stride)
+    try:
+        traced = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
+        ops.linear(ctx, x, w, traced)
+    finally:
+        lib.lib.b200_stream_gemm_trace(None, 0, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(traced, plain)
+    assert int(ctx.err.item()) == 0
+    data = buffer.cpu().numpy().reshape(-1, stamps)
+    blocks = data[data[:, 0] != 0]
+    assert len(blocks) >= (n + 127) // 128  # at least one block per 128 rows of W
+    for row in blocks:
+        seen = row[row != 0]  # a block without a cluster leaves the cluster's points empty
+        assert len(seen) >= stamps - 2 and all(a <= b for a, b in zip(seen, seen[1:])), row
+    # A later launch records nothing once the trace is off.
+    buffer.zero_()
+    ops.linear(ctx, x, w, traced)
+    torch.cuda.synchronize()
+    assert int(buffer.abs().sum().item()) == 0
+
+
 def paged_layout(seq_lens, page_size, extra_pages=3, seed=0):
     """Random, non-contiguous page assignment; returns (tables [S, max_pages], num_pages)."""
     rng = np.random.default_rng(seed)
