@@ -210,6 +210,9 @@ def test_tcgen05_gemm_takes_up_to_256_rows(lib, m, n, k):
     out = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
     ops.linear(ctx, x, w, out)
     torch.testing.assert_close(out.double(), x.double() @ w.double().T, atol=1e-4, rtol=1e-4)
+    rounded = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.linear(ctx, x, w, rounded)
+    assert torch.equal(rounded, out.to(torch.bfloat16))  # the same sums, rounded once
     act = torch.full((m, n // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
     assert ops.linear_swiglu(ctx, x, w, act)
     want = x.double() @ w.double().T
